@@ -56,6 +56,7 @@ class PositionSpec:
 
 @dataclass(frozen=True)
 class NormSpec:
+    """kind "rmsnorm": a gain per coordinate; "rmsnorm_scalar": one gain for all coordinates."""
     kind: str = "rmsnorm"
     eps: float = 1e-5
 
@@ -127,12 +128,20 @@ class LayerSpec:
 
     arrangement "pre_norm":  h += mixer(norm1(h)); h += ffn(norm2(h))
     (src/model/llama.cpp:324-379).
+    arrangement "parallel":  x = norm1(h); h += mixer(x) + ffn(x) - one norm, read by both; such a
+    layer has no ``ffn_norm`` and may have no feed-forward at all (both None).
+    ``extra`` carries the arrangement's own constants (for instance the width of a per-layer token
+    input that it adds after the feed-forward).
     """
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
-    ffn_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
     arrangement: str = "pre_norm"
+    extra: Tuple[Tuple[str, Any], ...] = ()
+
+    def extra_dict(self) -> Dict[str, Any]:
+        return dict(self.extra)
 
 
 @dataclass(frozen=True)

@@ -10,7 +10,8 @@ Adding an architecture = one ``register_architecture`` call with
   * ``parse_config(raw: dict) -> ModelConfig``: reads the architecture's own keys;
   * ``tensor_name(scope: tuple, slot: str) -> str``: the safetensors name of a part's
     weight slot.  Scopes are ("embedding",), ("lm_head",), ("final_norm",) and
-    ("layer", i, "mixer" | "feed_forward" | "mixer_norm" | "ffn_norm");
+    ("layer", i, "mixer" | "feed_forward" | "mixer_norm" | "ffn_norm" | "block") - "block" holds
+    the weights of the arrangement itself, if its class has ``weight_slots``;
   * optionally ``ignored_tensors``: name patterns (fnmatch) of tensors that exporters of this
     architecture store beside the weights and that nothing reads (buffers such as a rotary
     table); the loader passes over them instead of reporting them as unexpected.
@@ -78,6 +79,9 @@ def part(category: str, kind: str) -> type:
 
 
 def architecture_name_of(raw: Dict[str, Any]) -> str:
+    """The name under "architectures" (a list, the first entry counts) or "architecture" (one name)."""
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must be a non-empty list of names")

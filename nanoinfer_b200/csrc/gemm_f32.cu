@@ -13,7 +13,12 @@
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
-                int M, int N, int K) {
+                int M, int N, int K, int ldx, int ldo) {
+    // one product per blockIdx.z (a head): its activations are columns [z K, (z+1) K) of x, its
+    // matrix is w[z], its results are columns [z N, (z+1) N) of out
+    x += (size_t)blockIdx.z * K;
+    w += (size_t)blockIdx.z * N * K;
+    out += (size_t)blockIdx.z * N;
     __shared__ float xs[GF_BK][GF_BM + 4];
     __shared__ float ws[GF_BK][GF_BN + 4];
     const int m0 = blockIdx.y * GF_BM, n0 = blockIdx.x * GF_BN;
@@ -31,7 +36,7 @@ gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
             const int idx = threadIdx.x + 256 * e;
             const int r = idx >> 4, kk = idx & 15;
             const int k = k0 + kk;
-            xs[kk][r] = (m0 + r < M && k < K) ? x[(size_t)(m0 + r) * K + k] : 0.f;
+            xs[kk][r] = (m0 + r < M && k < K) ? x[(size_t)(m0 + r) * ldx + k] : 0.f;
             ws[kk][r] = (n0 + r < N && k < K) ? w[(size_t)(n0 + r) * K + k] : 0.f;
         }
         __syncthreads();
@@ -56,7 +61,7 @@ gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) out[(size_t)m * N + n] = acc[i][j];
+            if (n < N) out[(size_t)m * ldo + n] = acc[i][j];
         }
     }
 }
@@ -67,6 +72,20 @@ NI_EXPORT int ni_gemm_f32(const float* x, const float* w, float* out, int M, int
     if (K <= 0) return NI_ERR_BAD_ARGUMENT;
     dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
     if (grid.y > 65535) return NI_ERR_UNSUPPORTED_SIZE;
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, out, M, N, K);
+    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, out, M, N, K, K, N);
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// One product per head: out[m, h, :] = x[m, h, :] . w[h]^T with x [M, H, K] (rows ldx floats apart: it may
+// be some columns of a wider matrix), w [H, N, K], out [M, H, N], each output element the same ascending
+// chain of fused multiply-adds as above.
+NI_EXPORT int ni_gemm_f32_heads(const float* x, int ldx, const float* w, float* out, int M, int N, int K, int H,
+                                cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || H <= 0) return NI_OK;
+    if (K <= 0) return NI_ERR_BAD_ARGUMENT;
+    dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM, H);
+    if (grid.y > 65535 || H > 65535) return NI_ERR_UNSUPPORTED_SIZE;
+    if (ldx < H * K) return NI_ERR_BAD_ARGUMENT;
+    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, out, M, N, K, ldx, H * N);
     NI_RETURN_LAUNCH_STATUS();
 }

@@ -1,0 +1,74 @@
+// Latent attention keeps ONE compressed vector per token: c = RMSNorm(W_dkv x) (plain weight).
+// Keys and values of every head are products of c (k = W_uk c, v = W_uv c), so the attention
+// itself can run over the latents: the query is carried into the latent space (W_uk^T q, per
+// head), scores and the weighted sum are taken over the pages of c, and the result leaves
+// through W_uv.  These are the two small kernels around that: the normed write of a step's
+// latents into their pages, and the per-head output gate.
+#include "common.cuh"
+
+// pages[page, in_page, :] = x / sqrt(mean(x^2) + eps) * weight, x = columns [col0, col0 + R) of proj[t].
+// pages: [P, page_size, R]; the token's page comes from its request's block table.
+template <typename T>
+__global__ void latent_norm_write_kernel(const T* __restrict__ proj, int ld, int col0, const float* __restrict__ weight,
+                                         float eps, T* __restrict__ pages, const int* __restrict__ positions,
+                                         const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                         int bt_stride, int R, int page_size) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const T* x = proj + (size_t)t * ld + col0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        const float v = ni_to_float(x[i]);
+        ss += v * v;
+    }
+    ss = ni_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)R + eps);
+    const int pos = positions[t];
+    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+    T* dst = pages + ((size_t)page * page_size + pos % page_size) * R;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = ni_from_float<T>(ni_to_float(x[i]) * inv * weight[i]);
+}
+
+NI_EXPORT int ni_latent_norm_write(const void* proj, int dtype, int ld, int col0, const float* weight, float eps,
+                                   void* pages, const int* positions, const int* seq_of_token, const int* block_table,
+                                   int bt_stride, int n_tokens, int R, int page_size, cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (R <= 0 || page_size <= 0 || col0 < 0 || col0 + R > ld) return NI_ERR_BAD_ARGUMENT;
+    const int threads = R >= 1024 ? 256 : 128;
+#define LAUNCH(T)                                                                                              \
+    latent_norm_write_kernel<T><<<n_tokens, threads, 0, stream>>>((const T*)proj, ld, col0, weight, eps, (T*)pages, \
+                                                                  positions, seq_of_token, block_table, bt_stride, R, page_size)
+    if (dtype == NI_DTYPE_F32) LAUNCH(float);
+    else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);
+    else return NI_ERR_BAD_ARGUMENT;
+#undef LAUNCH
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// x[t, h, :] *= sigmoid(proj[t, col0 + h]);  x [T, H, V]
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ proj, int ld, int col0, int n_tokens, int H,
+                                 int V) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_tokens * H * V) return;
+    const long long th = idx / V;
+    const int t = (int)(th / H), h = (int)(th - (long long)t * H);
+    const float g = 1.0f / (1.0f + expf(-ni_to_float(proj[(size_t)t * ld + col0 + h])));
+    x[idx] = ni_from_float<T>(ni_to_float(x[idx]) * g);
+}
+
+NI_EXPORT int ni_head_gate(void* x, int dtype, const void* proj, int ld, int col0, int n_tokens, int H, int V,
+                           cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (H <= 0 || V <= 0 || col0 < 0 || col0 + H > ld) return NI_ERR_BAD_ARGUMENT;
+    const long long blocks = ((long long)n_tokens * H * V + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+    if (dtype == NI_DTYPE_F32)
+        head_gate_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)x, (const float*)proj, ld, col0, n_tokens, H, V);
+    else if (dtype == NI_DTYPE_BF16)
+        head_gate_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)proj, ld,
+                                                                        col0, n_tokens, H, V);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}

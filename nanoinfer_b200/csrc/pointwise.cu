@@ -1,0 +1,168 @@
+// Row-wise kernels that several designs share: an embedding with a sinusoidal position vector,
+// a cast of the FP32 residual stream to the compute dtype, a normed addition into the stream, the
+// PolyNorm activation, and a gate multiplied by a per-token table row.
+//
+// All statistics, angles and activation arguments are FP32; inputs and outputs are FP32 or
+// bfloat16 as their tensors say.  One block per row, sums in a fixed order, so a row's result
+// never depends on what else is in the step.
+#include "common.cuh"
+
+// out[t, 2i] = table[tok, 2i] + sin(p * f_i), out[t, 2i+1] = table[tok, 2i+1] + cos(p * f_i),
+// with p = positions[t] and f_i = inv_freq[i] (computed on the host, rounded once to FP32).
+template <typename T>
+__global__ void embedding_sinusoid_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
+                                          const T* __restrict__ table, const float* __restrict__ inv_freq,
+                                          float* __restrict__ out, int d, int vocab) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    const bool ok = tok >= 0 && tok < vocab;
+    const T* row = table + (size_t)(ok ? tok : 0) * d;
+    const float p = (float)positions[t];
+    float* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float ang = __fmul_rn(p, inv_freq[i >> 1]);
+        const float pe = (i & 1) ? cosf(ang) : sinf(ang);
+        o[i] = (ok ? ni_to_float(row[i]) : 0.f) + pe;
+    }
+}
+
+NI_EXPORT int ni_embedding_sinusoid(const int* tokens, const int* positions, const void* table, int table_dtype,
+                                    const float* inv_freq, float* out, int n_tokens, int d, int vocab,
+                                    cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (d <= 0 || vocab <= 0) return NI_ERR_BAD_ARGUMENT;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == NI_DTYPE_F32)
+        embedding_sinusoid_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, positions, (const float*)table,
+                                                                           inv_freq, out, d, vocab);
+    else if (table_dtype == NI_DTYPE_BF16)
+        embedding_sinusoid_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            tokens, positions, (const __nv_bfloat16*)table, inv_freq, out, d, vocab);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// out = bfloat16(x), element by element (x FP32).
+__global__ void cast_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(x[i]);
+}
+
+NI_EXPORT int ni_cast_bf16(const float* x, void* out, long long n, cudaStream_t stream) {
+    if (n <= 0) return NI_OK;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+    cast_bf16_kernel<<<(int)blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out, n);
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// h[t, :] += y[t, :] / sqrt(mean(y[t, :]^2) + eps) * weight
+template <typename T>
+__global__ void add_normed_kernel(float* __restrict__ h, const T* __restrict__ y, const float* __restrict__ weight,
+                                  float eps, int d) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const T* yr = y + (size_t)t * d;
+    float* hr = h + (size_t)t * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = ni_to_float(yr[i]);
+        ss += v * v;
+    }
+    ss = ni_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) hr[i] += ni_to_float(yr[i]) * inv * weight[i];
+}
+
+NI_EXPORT int ni_add_normed(float* h, const void* y, int y_dtype, const float* weight, float eps, int n_rows, int d,
+                            cudaStream_t stream) {
+    if (n_rows <= 0) return NI_OK;
+    if (d <= 0) return NI_ERR_BAD_ARGUMENT;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (y_dtype == NI_DTYPE_F32)
+        add_normed_kernel<float><<<n_rows, threads, 0, stream>>>(h, (const float*)y, weight, eps, d);
+    else if (y_dtype == NI_DTYPE_BF16)
+        add_normed_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(h, (const __nv_bfloat16*)y, weight, eps, d);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// PolyNorm: out = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(v) = v / sqrt(mean(v^2) + eps)
+// over the row.  coef = {a, b, c, e} (FP32 on the device).
+template <typename T>
+__global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps,
+                                T* __restrict__ out, int n) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const T* zr = z + (size_t)t * n;
+    T* o = out + (size_t)t * n;
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = ni_to_float(zr[i]);
+        const float v2 = v * v;
+        s1 += v2;
+        s2 += v2 * v2;
+        s3 += (v2 * v) * (v2 * v);
+    }
+    s1 = ni_block_sum(s1, scratch);
+    s2 = ni_block_sum(s2, scratch);
+    s3 = ni_block_sum(s3, scratch);
+    const float r1 = coef[0] / sqrtf(s1 / (float)n + eps);
+    const float r2 = coef[1] / sqrtf(s2 / (float)n + eps);
+    const float r3 = coef[2] / sqrtf(s3 / (float)n + eps);
+    const float e = coef[3];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = ni_to_float(zr[i]);
+        const float v2 = v * v;
+        o[i] = ni_from_float<T>(v * r1 + v2 * r2 + (v2 * v) * r3 + e);
+    }
+}
+
+NI_EXPORT int ni_polynorm(const void* z, int dtype, const float* coef, float eps, void* out, int n_rows, int n,
+                          cudaStream_t stream) {
+    if (n_rows <= 0) return NI_OK;
+    if (n <= 0) return NI_ERR_BAD_ARGUMENT;
+    const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+    if (dtype == NI_DTYPE_F32)
+        polynorm_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)z, coef, eps, (float*)out, n);
+    else if (dtype == NI_DTYPE_BF16)
+        polynorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)z, coef, eps,
+                                                                      (__nv_bfloat16*)out, n);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// out[t, j] = gelu_tanh(gate[t, j]) * table[tokens[t], first + j],  j < n; the table has `stride` columns.
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <typename T, typename TT>
+__global__ void gelu_table_gate_kernel(const T* __restrict__ gate, const int* __restrict__ tokens,
+                                       const TT* __restrict__ table, T* __restrict__ out, int n_rows, int n,
+                                       int first, int stride, int vocab) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_rows * n) return;
+    const int t = (int)(idx / n), j = (int)(idx - (long long)t * n);
+    const int tok = tokens[t];
+    const float e = (tok >= 0 && tok < vocab) ? ni_to_float(table[(size_t)tok * stride + first + j]) : 0.f;
+    const float z = ni_to_float(gate[idx]);
+    const float g = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    out[idx] = ni_from_float<T>(g * e);
+}
+
+NI_EXPORT int ni_gelu_table_gate(const void* gate, int dtype, const int* tokens, const void* table, int table_dtype,
+                                 void* out, int n_rows, int n, int first, int stride, int vocab, cudaStream_t stream) {
+    if (n_rows <= 0 || n <= 0) return NI_OK;
+    if (first < 0 || first + n > stride || vocab <= 0) return NI_ERR_BAD_ARGUMENT;
+    const long long blocks = ((long long)n_rows * n + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+#define LAUNCH(T, TT)                                                                                          \
+    gelu_table_gate_kernel<T, TT><<<(int)blocks, 256, 0, stream>>>((const T*)gate, tokens, (const TT*)table, \
+                                                                   (T*)out, n_rows, n, first, stride, vocab)
+    if (dtype == NI_DTYPE_F32 && table_dtype == NI_DTYPE_F32) LAUNCH(float, float);
+    else if (dtype == NI_DTYPE_BF16 && table_dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return NI_ERR_BAD_ARGUMENT;
+#undef LAUNCH
+    NI_RETURN_LAUNCH_STATUS();
+}

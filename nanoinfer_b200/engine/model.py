@@ -28,6 +28,8 @@ class DecoderModel:
         for i, layer in enumerate(config.layers):
             cls = registry.part("arrangement", layer.arrangement)
             self.blocks.append(cls(layer, d, lambda what, i=i: by_scope.get(("layer", i, what), {}), rt))
+            if hasattr(self.blocks[-1], "bind_embedding"):     # a block that reads a table the embedding owns
+                self.blocks[-1].bind_embedding(self.embedding)
         self.final_norm = registry.part("norm", config.final_norm.kind)(
             config.final_norm, d, by_scope.get(("final_norm",), {}), rt)
         head = config.head_spec()
@@ -70,7 +72,10 @@ class DecoderModel:
             if self._fused is not None and self._fused.takes(ctx):
                 return self._fused.run(ctx)      # a step of a few single tokens: one persistent kernel
         h = rt.empty(ctx.n_tokens, cfg.hidden_size, dtype=torch.float32)
-        self.embedding.forward(ctx.tokens, h)
+        if getattr(self.embedding, "wants_context", False):
+            self.embedding.forward(ctx.tokens, h, ctx)         # an embedding that reads positions
+        else:
+            self.embedding.forward(ctx.tokens, h)
         delta = None
         for r, run in enumerate(cfg.schedule):
             ctx.read_after, ctx.norm_after = self._read_after[r], self._norm_after[r]

@@ -157,6 +157,19 @@ class Runtime:
             return out
         return ops.linear_bf16(x, w, out_dtype, residual, warm, handoff)
 
+    def heads_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """One product per head: y[t, h, :] = x[t, h, :] . w[h]^T for x [T, H K] (some columns of a wider
+        matrix will do) and w [H, N, K]; returns [T, H N] in the compute dtype.  float32: the package's FFMA kernel, one ascending chain per
+        element; bfloat16: a library batched product (FP32 accumulation) written straight into y."""
+        n_heads, n, k = w.shape
+        t = x.shape[0]
+        y = self.empty(t, n_heads * n)
+        if self.dtype == torch.float32:
+            ops.gemm_f32_heads(x, w, y)
+        else:
+            torch.bmm(x.view(t, n_heads, k).transpose(0, 1), w.transpose(1, 2), out=y.view(t, n_heads, n).transpose(0, 1))
+        return y
+
     def skinny(self, n_rows: int, k: int) -> bool:
         """True if a product of n_rows activations with inner size k goes to the package's own
         bandwidth kernel (and so may carry fused prologues and epilogues)."""

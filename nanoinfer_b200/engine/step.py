@@ -207,6 +207,12 @@ class ModelRunner:
                               ["gemv_bf16", "gemv_ksplit", "gemm_tc", "gemm_tc2", "gemm_swap_tc", "attention_prefill", "attention_prefill_tc", "attention_decode"]
                               + (["decode_fused"] if fused_decode else [])))
         self.model = DecoderModel(config, weights, self.rt)
+        # libraries that only some parts use (a part names them in ``kernel_modules``): built together, now
+        extra = sorted({m for b in self.model.blocks for p in (b, getattr(b, "mixer", None), getattr(b, "feed_forward", None))
+                        for m in getattr(p, "kernel_modules", ())}
+                       | set(getattr(self.model.embedding, "kernel_modules", ())))
+        if extra:
+            ops.preload(extra)
 
         # cache groups: one per distinct need among the runs that own a cache
         needs = self.model.cache_needs()

@@ -38,6 +38,23 @@ _SIGNATURES = {
     },
     "gemm_f32": {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
+        "ni_gemm_f32_heads": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
+    },
+    "pointwise": {
+        "ni_embedding_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
+        "ni_cast_bf16": [_P, _P, _LL, _P],
+        "ni_add_normed": [_P, _P, _I, _P, _F, _I, _I, _P],
+        "ni_polynorm": [_P, _I, _P, _F, _P, _I, _I, _P],
+        "ni_gelu_table_gate": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+    },
+    "delta_rule": {
+        "ni_delta_prepare": [_P, _P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+        "ni_delta_recurrence": [_P, _P, _P, _P, _LL, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "ni_delta_gated_norm": [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+    },
+    "latent": {
+        "ni_latent_norm_write": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "ni_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
     },
     "gemv_bf16": {
         "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _I, _P, _I, _F, _P],
@@ -327,6 +344,132 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("gemm_f32: shapes do not agree")
     _check(load("gemm_f32").ni_gemm_f32(_dev(x, "x", torch.float32), _dev(w, "w", torch.float32),
                                         _dev(out, "out", torch.float32), m, n, k, _stream()), "gemm_f32")
+
+
+def gemm_f32_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """One product per head, plain FP32: out[m, h, :] = x[m, h, :] . w[h]^T with x [M, H K] (its rows may
+    be some columns of a wider matrix), w [H, N, K], out [M, H N], all float32."""
+    h, n, k = w.shape
+    m = x.shape[0]
+    if x.shape != (m, h * k) or out.shape != (m, h * n):
+        raise KernelError("gemm_f32_heads: shapes do not agree")
+    if not x.is_cuda or x.dtype != torch.float32 or x.stride(1) != 1 or x.stride(0) < h * k:
+        raise KernelError("gemm_f32_heads: x must be float32 rows on the device, each row contiguous")
+    _check(load("gemm_f32").ni_gemm_f32_heads(x.data_ptr(), x.stride(0), _dev(w, "w", torch.float32),
+                                              _dev(out, "out", torch.float32), m, n, k, h, _stream()), "gemm_f32_heads")
+
+
+def embedding_sinusoid(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, inv_freq: torch.Tensor,
+                       out: torch.Tensor) -> None:
+    """out[t, 2i] = table[tokens[t], 2i] + sin(p f_i), out[t, 2i+1] = table[tokens[t], 2i+1] + cos(p f_i) with
+    p = positions[t], f = inv_freq float32 [ceil(d / 2)]; out float32 [T, d]."""
+    n, d = out.shape
+    if tokens.numel() != n or positions.numel() != n or table.shape[1] != d or inv_freq.numel() != (d + 1) // 2:
+        raise KernelError("embedding_sinusoid: shapes do not agree")
+    _check(load("pointwise").ni_embedding_sinusoid(
+        _dev(tokens, "tokens", torch.int32), _dev(positions, "positions", torch.int32), _dev(table, "table"),
+        _code(table, "table"), _dev(inv_freq, "inv_freq", torch.float32), _dev(out, "out", torch.float32), n, d,
+        table.shape[0], _stream()), "embedding_sinusoid")
+
+
+def cast_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = bfloat16(x) for float32 x of the same shape."""
+    if x.shape != out.shape:
+        raise KernelError("cast_bf16: shapes do not agree")
+    _check(load("pointwise").ni_cast_bf16(_dev(x, "x", torch.float32), _dev(out, "out", torch.bfloat16), x.numel(),
+                                          _stream()), "cast_bf16")
+
+
+def add_normed(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """h += y / sqrt(mean(y^2) + eps) * weight, row by row; h float32 [T, d], weight float32 [d]."""
+    n, d = h.shape
+    if y.shape != h.shape or weight.numel() != d:
+        raise KernelError("add_normed: shapes do not agree")
+    _check(load("pointwise").ni_add_normed(_dev(h, "h", torch.float32), _dev(y, "y"), _code(y, "y"),
+                                           _dev(weight, "weight", torch.float32), float(eps), n, d, _stream()), "add_normed")
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps); coef = (a, b, c, e)
+    float32 on the device; z and out [T, n] of one dtype."""
+    if z.shape != out.shape or z.dtype != out.dtype or coef.numel() != 4:
+        raise KernelError("polynorm: shapes or dtypes do not agree")
+    _check(load("pointwise").ni_polynorm(_dev(z, "z"), _code(z, "z"), _dev(coef, "coef", torch.float32), float(eps),
+                                         _dev(out, "out"), z.shape[0], z.shape[1], _stream()), "polynorm")
+
+
+def gelu_table_gate(gate: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, first: int, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(gate[t, j]) * table[tokens[t], first + j]; gate, out [T, n]; table [vocab, stride]."""
+    n_rows, n = gate.shape
+    if out.shape != gate.shape or out.dtype != gate.dtype or table.dtype != gate.dtype or tokens.numel() != n_rows:
+        raise KernelError("gelu_table_gate: shapes or dtypes do not agree")
+    _check(load("pointwise").ni_gelu_table_gate(
+        _dev(gate, "gate"), _code(gate, "gate"), _dev(tokens, "tokens", torch.int32), _dev(table, "table"),
+        _code(table, "table"), _dev(out, "out"), n_rows, n, int(first), table.shape[1], table.shape[0], _stream()),
+        "gelu_table_gate")
+
+
+def delta_prepare(proj, conv_w, a_log, dt_bias, state, seq_of_token, cu_q, slots, n_seqs, n_q_heads_kv, n_heads, dim,
+                  vdim, taps, qkv, beta, decay) -> None:
+    """The gated delta rule's per-token inputs from the fused projection ``proj`` (float32 [T, ld], columns
+    q | k | v | gate | b | a): convolution + silu, unit q and k, beta, decay; then each request's new
+    convolution history in ``state`` (float32 [slots, H D V + (taps - 1) C])."""
+    n = proj.shape[0]
+    c = 2 * n_q_heads_kv * dim + n_heads * vdim
+    if qkv.shape != (n, c) or beta.shape != (n, n_heads) or decay.shape != (n, n_heads) or conv_w.shape != (c, taps):
+        raise KernelError("delta_prepare: shapes do not agree")
+    if state.shape[1] != n_heads * dim * vdim + (taps - 1) * c:
+        raise KernelError("delta_prepare: the state has another size")
+    f32 = torch.float32
+    _check(load("delta_rule").ni_delta_prepare(
+        _dev(proj, "proj", f32), _dev(conv_w, "conv_w", f32), _dev(a_log, "a_log", f32), _dev(dt_bias, "dt_bias", f32),
+        _dev(state, "state", f32), state.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
+        _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), n, n_seqs, n_q_heads_kv, n_heads, dim, vdim,
+        taps, proj.shape[1], _dev(qkv, "qkv", f32), _dev(beta, "beta", f32), _dev(decay, "decay", f32), _stream()),
+        "delta_prepare")
+
+
+def delta_recurrence(qkv, beta, decay, state, cu_q, slots, n_seqs, n_q_heads_kv, n_heads, dim, vdim, out) -> None:
+    """S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q for every token of every request, in order;
+    S float32 [H, D, V] at the start of each row of ``state``; out float32 [T, H V]."""
+    f32 = torch.float32
+    if out.shape != (qkv.shape[0], n_heads * vdim):
+        raise KernelError("delta_recurrence: out must be [T, H V]")
+    _check(load("delta_rule").ni_delta_recurrence(
+        _dev(qkv, "qkv", f32), _dev(beta, "beta", f32), _dev(decay, "decay", f32), _dev(state, "state", f32),
+        state.shape[1], _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), n_seqs, n_q_heads_kv,
+        n_heads, dim, vdim, _dev(out, "out", f32), _stream()), "delta_recurrence")
+
+
+def delta_gated_norm(o, proj, weight, eps, n_q_heads_kv, n_heads, dim, vdim, y) -> None:
+    """y[t, h, :] = o[t, h, :] / rms * weight * silu(gate[t, h, :]), gate = its columns of ``proj``."""
+    n = o.shape[0]
+    if y.shape != o.shape or weight.numel() != vdim:
+        raise KernelError("delta_gated_norm: shapes do not agree")
+    _check(load("delta_rule").ni_delta_gated_norm(
+        _dev(o, "o", torch.float32), _dev(proj, "proj", torch.float32), _dev(weight, "weight", torch.float32), float(eps),
+        n, n_q_heads_kv, n_heads, dim, vdim, proj.shape[1], _dev(y, "y"), _code(y, "y"), _stream()), "delta_gated_norm")
+
+
+def latent_norm_write(proj, col0, rank, weight, eps, pages, positions, seq_of_token, block_table, page_size) -> None:
+    """pages[page of t, place of t, :] = RMSNorm(proj[t, col0 : col0 + rank]) * weight; pages [P, page_size, rank]."""
+    n = proj.shape[0]
+    if tuple(pages.shape[1:]) != (page_size, rank) or pages.dtype != proj.dtype or weight.numel() != rank:
+        raise KernelError("latent_norm_write: pages must be [P, page_size, rank] of proj's dtype")
+    _check(load("latent").ni_latent_norm_write(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], int(col0), _dev(weight, "weight", torch.float32),
+        float(eps), _dev(pages, "pages"), _dev(positions, "positions", torch.int32),
+        _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], n, rank, page_size, _stream()), "latent_norm_write")
+
+
+def head_gate(x, proj, col0, n_heads, vdim) -> None:
+    """x[t, h, :] *= sigmoid(proj[t, col0 + h]) in place; x [T, H V]."""
+    n = x.shape[0]
+    if x.shape[1] != n_heads * vdim or proj.shape[0] != n or proj.dtype != x.dtype:
+        raise KernelError("head_gate: shapes or dtypes do not agree")
+    _check(load("latent").ni_head_gate(_dev(x, "x"), _code(x, "x"), _dev(proj, "proj"), proj.shape[1], int(col0), n,
+                                       n_heads, vdim, _stream()), "head_gate")
 
 
 GEMV_MAX_ROWS = 16      # what the skinny kernels take

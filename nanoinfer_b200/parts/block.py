@@ -6,7 +6,9 @@ from typing import Optional
 import torch
 
 from ..config.registry import part, register_part
+from ..kernels import ops
 from ..kernels.ops import NormHandoff
+from .base import WeightSlot
 
 
 class PreNormBlock:
@@ -90,4 +92,97 @@ def _fuses(part_obj, norm, n_rows: int) -> bool:
     return hasattr(part_obj, "forward_fused_norm") and part_obj.can_fuse_norm(norm, n_rows)
 
 
+class ParallelBlock:
+    """x = norm(h);  h += mixer(x) + ffn(x): one norm, read by both sublayers (a layer may have no
+    feed-forward).  Optionally followed by a per-layer token input (``token_input_dim`` = n > 0 in the
+    layer's extra, with ``token_input_index`` = i):
+
+        e = table[token, i n : (i + 1) n];  y = W_proj (gelu_tanh(W_gate h) * e);  h += RMSNorm(y) * weight
+
+    where h is the stream after the sublayers' additions, the table [vocab, layers * n] belongs to the
+    embedding (``layer_table``), and the norm has a plain weight and the eps ``token_input_eps``.  The
+    additions into the stream, the norm's statistics and the gate's activation are FP32."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    @staticmethod
+    def weight_slots(layer_spec, hidden_size: int):
+        n = int(layer_spec.extra_dict().get("token_input_dim", 0))
+        if n <= 0:
+            return {}
+        return {"gate": WeightSlot((n, hidden_size)), "proj": WeightSlot((hidden_size, n)),
+                "norm": WeightSlot((hidden_size,), init="ones")}
+
+    def __init__(self, layer_spec, hidden_size: int, weights_of, rt) -> None:
+        self.rt, self.hidden_size = rt, hidden_size
+        self.mixer_norm = part("norm", layer_spec.mixer_norm.kind)(
+            layer_spec.mixer_norm, hidden_size, weights_of("mixer_norm"), rt)
+        self.mixer = part("mixer", layer_spec.mixer.kind)(layer_spec.mixer, hidden_size, weights_of("mixer"), rt)
+        self.feed_forward = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = part("feed_forward", layer_spec.feed_forward.kind)(
+                layer_spec.feed_forward, hidden_size, weights_of("feed_forward"), rt)
+        extra = layer_spec.extra_dict()
+        self.input_dim = int(extra.get("token_input_dim", 0))
+        self.input_first = int(extra.get("token_input_index", 0)) * self.input_dim
+        self.input_eps = float(extra.get("token_input_eps", 1e-6))
+        self.table = None
+        if self.input_dim > 0:
+            w = weights_of("block")
+            self.w_gate, self.w_proj = rt.weight(w["gate"]), rt.weight(w["proj"])
+            self.input_gain = rt.gain(w["norm"])
+
+    def bind_embedding(self, embedding) -> None:
+        """The token inputs of all layers are one table, owned by the embedding."""
+        if self.input_dim <= 0:
+            return
+        table = getattr(embedding, "layer_table", None)
+        if table is None or table.shape[1] < self.input_first + self.input_dim:
+            raise ValueError("a layer with a token input needs an embedding whose layer_table holds its columns")
+        self.table = table
+
+    def weights_in_order(self) -> tuple:
+        ffn = self.feed_forward
+        return tuple(getattr(self.mixer, "weights_in_order", tuple)()) + \
+            (tuple(getattr(ffn, "weights_in_order", tuple)()) if ffn is not None else ())
+
+    def first_norm(self):
+        return None
+
+    def forward(self, h: torch.Tensor, delta, ctx, cache):
+        if isinstance(delta, NormHandoff):
+            delta = None                                   # the stream is up to date; this norm is computed here
+        x = self.mixer_norm.forward(h, delta)
+        pending = []
+        for sub, args in ((self.mixer, (x, ctx, cache)), (self.feed_forward, (x, ctx))):
+            if sub is None:
+                continue
+            if getattr(sub, "adds_into_residual", False):
+                y = sub.forward(*args, residual=h)         # may add in place and return None
+            else:
+                y = sub.forward(*args)
+            if y is not None:
+                pending.append(y)
+        for y in pending:                                  # both sublayers have read x by now
+            ops.residual_add(h, y)
+        if self.input_dim > 0:
+            self._token_input(h, ctx)
+        return None
+
+    def _token_input(self, h: torch.Tensor, ctx) -> None:
+        rt = self.rt
+        n = h.shape[0]
+        if rt.dtype == torch.float32:
+            hc = h
+        else:
+            hc = rt.empty(n, self.hidden_size)
+            ops.cast_bf16(h, hc)
+        gate = rt.linear(hc, self.w_gate)
+        gated = rt.empty(n, self.input_dim)
+        ops.gelu_table_gate(gate, ctx.tokens, self.table, self.input_first, gated)
+        y = rt.linear(gated, self.w_proj, out_dtype=torch.float32)
+        ops.add_normed(h, y, self.input_gain, self.input_eps)
+
+
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)
+register_part("arrangement", "parallel", ParallelBlock, replace=True)

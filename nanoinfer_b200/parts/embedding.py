@@ -1,6 +1,9 @@
 """Embeddings: how a step's token ids become rows of the FP32 residual stream."""
 from __future__ import annotations
 
+import numpy as np
+import torch
+
 from ..config.registry import register_part
 from ..kernels import ops
 from .base import Part, WeightSlot
@@ -28,4 +31,39 @@ class TableEmbedding(Part):
         ops.embedding(tokens, self.table, h)
 
 
+class SinusoidTableEmbedding(Part):
+    """Row ``id`` of a [vocab, hidden] table plus a sinusoidal position vector: entry 2i is
+    sin(p * base^(-2i / hidden)), entry 2i + 1 the cosine of the same angle (p = the token's position,
+    ``base`` from the spec's extra, 10000 by default).  Frequencies are computed once on the host in
+    double precision and rounded to FP32; angles and the sum are FP32 on the device.
+
+    With ``layer_inputs`` = n > 0 in the spec's extra it also owns a second table [vocab, n]: inputs that
+    the layers themselves read by token id (``layer_table``; a block takes its own columns of it)."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    graph_safe = "all"
+    wants_context = True        # forward(tokens, h, ctx): it reads the tokens' positions
+
+    @staticmethod
+    def weight_slots(spec, hidden_size):
+        slots = {"weight": WeightSlot((spec.vocab_size, hidden_size))}
+        n = int(spec.extra_dict().get("layer_inputs", 0))
+        if n > 0:
+            slots["layer_inputs"] = WeightSlot((spec.vocab_size, n))
+        return slots
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        self.table = rt.weight(weights["weight"])
+        self.layer_table = rt.weight(weights["layer_inputs"]) if "layer_inputs" in weights else None
+        base = float(spec.extra_dict().get("base", 10000.0))
+        i = np.arange((hidden_size + 1) // 2, dtype=np.float64)
+        self.inv_freq = torch.from_numpy(np.power(base, -2.0 * i / hidden_size).astype(np.float32)).to(rt.device)
+
+    def forward(self, tokens, h, ctx) -> None:
+        ops.embedding_sinusoid(tokens, ctx.positions, self.table, self.inv_freq, h)
+
+
 register_part("embedding", "table", TableEmbedding, replace=True)
+register_part("embedding", "table_sinusoid", SinusoidTableEmbedding, replace=True)

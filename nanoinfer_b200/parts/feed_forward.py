@@ -89,4 +89,39 @@ class SwiGLU(Part):
         return handoff if handoff is not None else out
 
 
+class PolyNorm(Part):
+    """y = down(act(up(x))) with act(z) = a N(z) + b N(z^2) + c N(z^3) + e: powers element by element,
+    N(v) = v / sqrt(mean(v^2) + eps) over a token's feed-forward values, four learned numbers (a, b, c, e).
+    The three means and the polynomial are FP32; ``eps`` comes in the spec's extra ("eps")."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = True
+    graph_safe = "all"
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        i = spec.intermediate_size
+        return {"up": WeightSlot((i, hidden_size)), "down": WeightSlot((hidden_size, i)), "act": WeightSlot((4,))}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        self.inter = spec.intermediate_size
+        self.eps = float(spec.extra_dict().get("eps", 1e-6))
+        self.w_up = rt.weight(weights["up"])
+        self.w_down = rt.weight(weights["down"])
+        self.coef = rt.gain(weights["act"])
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_up, self.w_down)
+
+    def forward(self, x: torch.Tensor, ctx, residual=None):
+        rt = self.rt
+        z = rt.linear(x, self.w_up)
+        act = rt.empty(x.shape[0], self.inter)
+        ops.polynorm(z, self.coef, self.eps, act)
+        return rt.linear(act, self.w_down, residual=residual)
+
+
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "polynorm", PolyNorm, replace=True)

@@ -9,10 +9,98 @@ import torch
 from ..config.model_config import ConfigError
 from ..config.registry import part, register_part
 from ..kernels import ops
-from .base import PagedKVNeed, Part, StepPlan, WeightSlot
+from .base import PagedKVNeed, PagedNeed, Part, StepPlan, WeightSlot
 
 
-class PagedAttention(Part):
+class PagedAttendMixin:
+    """What every mixer that attends over pages of keys and values shares: the step's plan (which tokens
+    go to which kernel) and the choice among the attention kernels.  A class that uses it sets n_heads,
+    n_kv, head_dim, window, scale, position and w_o."""
+
+    # How the attention kernels split a step.  Requests that bring at most SHORT_PORTION tokens are
+    # handled token by token by the split-K kernel (which fetches a token's last
+    # ops.DECODE_FRESH_KEYS keys late, after the kernel that writes them); longer portions go to the
+    # flash-style kernels in tiles of TILE_ROWS query rows, the tile with the most keys first.
+    SHORT_PORTION = ops.DECODE_FRESH_KEYS
+    TILE_ROWS = ops.PREFILL_TILE_ROWS
+
+    @staticmethod
+    def plan_step(q_lens: List[int], starts: List[int]) -> StepPlan:
+        """dec_tokens: token indices of the short portions; long_tokens: of the long ones;
+        tile_seq / tile_row0: request and first query row of each tile.  The arrays' sizes follow
+        from q_lens alone; the tiles' order also from the cached lengths."""
+        i32 = np.int32
+        if max(q_lens) == 1:       # single tokens only: the kernels take tokens 0 .. n-1 as they come
+            none = np.zeros(0, dtype=i32)
+            return StepPlan({"dec_tokens": none, "long_tokens": none, "tile_seq": none, "tile_row0": none},
+                            {"n_dec": len(q_lens), "n_tiles": 0})
+        dec, long_tok, tiles = [], [], []
+        at = 0
+        for i, (ql, start) in enumerate(zip(q_lens, starts)):
+            if ql <= PagedAttendMixin.SHORT_PORTION:
+                dec.extend(range(at, at + ql))
+            else:
+                long_tok.extend(range(at, at + ql))
+                tiles.extend((start + r0, i, r0) for r0 in range(0, ql, PagedAttendMixin.TILE_ROWS))
+            at += ql
+        tiles.sort(key=lambda x: -x[0])      # most keys first
+        return StepPlan({"dec_tokens": np.asarray(dec, dtype=i32), "long_tokens": np.asarray(long_tok, dtype=i32),
+                         "tile_seq": np.asarray([t[1] for t in tiles], dtype=i32),
+                         "tile_row0": np.asarray([t[2] for t in tiles], dtype=i32)},
+                        {"n_dec": len(dec), "n_tiles": len(tiles)})
+
+    def _attend(self, q, cache, att, ctx, table) -> None:
+        """Attention of every token of the step over its own request's pages.
+
+        float32: the plain kernel.  bfloat16: single query tokens (and portions of at most
+        two tokens) go to the split-K kernel, longer portions to the flash-style kernel;
+        head sizes those do not take fall back to the plain kernel, never to a wrong result."""
+        rt = self.rt
+        common = (self.n_heads, self.n_kv, self.head_dim, rt.page_size, self.window, self.scale)
+        n = q.shape[0]
+        slopes = getattr(self.position, "head_slopes", None)
+        if rt.dtype != torch.bfloat16 or slopes is not None:
+            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)):
+            # the plain kernel takes both; the tensor-core kernels know rotations only
+            ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
+                                  table, *common, head_slopes=slopes)
+            return
+        decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
+        prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM
+        plan = None if ctx.decode_only else ctx.plan_of(self)    # a step of single tokens needs no lists
+        n_dec = n if plan is None else plan.scalars["n_dec"]
+        dec_list = None if plan is None else plan.arrays["dec_tokens"]
+        if n_dec > 0:
+            if decode_ok and rt.balanced_attention(n_dec, self.n_kv, self.head_dim) and n_dec <= ops.DECODE_BALANCED_MAX_ITEMS:
+                # many tokens: their keys dealt evenly over a fixed set of blocks, whatever their lengths
+                scratch = rt.workspace("attention_decode_balanced_partials",
+                                       ops.attention_decode_balanced_scratch(self.n_heads, self.n_kv, self.head_dim), torch.float32)
+                tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
+                ops.attention_decode_balanced(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
+                                              ctx.seq_of_token, table, *common, scratch, tickets,
+                                              warm=rt.warm_attention(self.w_o, ctx))
+            elif decode_ok:
+                splits = ops.decode_splits(n_dec, self.n_kv, self.head_dim, ctx.max_kv_len)
+                scratch = rt.workspace("attention_decode_partials",
+                                       n_dec * self.n_heads * splits * (self.head_dim + 2), torch.float32)
+                tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
+                ops.attention_decode(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
+                                     ctx.seq_of_token, table, *common, splits, scratch, tickets,
+                                     warm=rt.warm_attention(self.w_o, ctx))
+            else:
+                ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
+                                      table, *common, token_list=dec_list)
+        if plan is not None and plan.scalars["n_tiles"] > 0:
+            if prefill_ok:
+                ops.attention_prefill(q, cache.k_pages, cache.v_pages, att, plan.arrays["tile_seq"],
+                                      plan.arrays["tile_row0"], plan.scalars["n_tiles"], ctx.cu_q, ctx.kv_len, table,
+                                      *common)
+            else:
+                ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
+                                      table, *common, token_list=plan.arrays["long_tokens"])
+
+
+class PagedAttention(PagedAttendMixin, Part):
     """Grouped-query attention: fused QKV projection, position encoding + cache write,
     attention over this request's pages, output projection.
 
@@ -63,38 +151,6 @@ class PagedAttention(Part):
 
     adds_into_residual = True   # forward() accepts residual= and may add its output there
     graph_safe = "all"          # everything that changes between steps is read from device memory
-
-    # How the attention kernels split a step.  Requests that bring at most SHORT_PORTION tokens are
-    # handled token by token by the split-K kernel (which fetches a token's last
-    # ops.DECODE_FRESH_KEYS keys late, after the kernel that writes them); longer portions go to the
-    # flash-style kernels in tiles of TILE_ROWS query rows, the tile with the most keys first.
-    SHORT_PORTION = ops.DECODE_FRESH_KEYS
-    TILE_ROWS = ops.PREFILL_TILE_ROWS
-
-    @staticmethod
-    def plan_step(q_lens: List[int], starts: List[int]) -> StepPlan:
-        """dec_tokens: token indices of the short portions; long_tokens: of the long ones;
-        tile_seq / tile_row0: request and first query row of each tile.  The arrays' sizes follow
-        from q_lens alone; the tiles' order also from the cached lengths."""
-        i32 = np.int32
-        if max(q_lens) == 1:       # single tokens only: the kernels take tokens 0 .. n-1 as they come
-            none = np.zeros(0, dtype=i32)
-            return StepPlan({"dec_tokens": none, "long_tokens": none, "tile_seq": none, "tile_row0": none},
-                            {"n_dec": len(q_lens), "n_tiles": 0})
-        dec, long_tok, tiles = [], [], []
-        at = 0
-        for i, (ql, start) in enumerate(zip(q_lens, starts)):
-            if ql <= PagedAttention.SHORT_PORTION:
-                dec.extend(range(at, at + ql))
-            else:
-                long_tok.extend(range(at, at + ql))
-                tiles.extend((start + r0, i, r0) for r0 in range(0, ql, PagedAttention.TILE_ROWS))
-            at += ql
-        tiles.sort(key=lambda x: -x[0])      # most keys first
-        return StepPlan({"dec_tokens": np.asarray(dec, dtype=i32), "long_tokens": np.asarray(long_tok, dtype=i32),
-                         "tile_seq": np.asarray([t[1] for t in tiles], dtype=i32),
-                         "tile_row0": np.asarray([t[2] for t in tiles], dtype=i32)},
-                        {"n_dec": len(dec), "n_tiles": len(tiles)})
 
     def can_fuse_norm(self, norm, n_rows: int) -> bool:
         """True if forward_fused_norm can take the residual stream itself (few rows, bfloat16)."""
@@ -149,55 +205,93 @@ class PagedAttention(Part):
                         warm=rt.warm_after(ctx, skip=rt.attention_share(ctx), which=1) if ctx.decode_only else None)
         return handoff if handoff is not None else out
 
-    def _attend(self, q, cache, att, ctx, table) -> None:
-        """Attention of every token of the step over its own request's pages.
 
-        float32: the plain kernel.  bfloat16: single query tokens (and portions of at most
-        two tokens) go to the split-K kernel, longer portions to the flash-style kernel;
-        head sizes those do not take fall back to the plain kernel, never to a wrong result."""
+class _KeyValuePages:
+    """What the attention kernels read of a cache: key pages and value pages [P, Hkv, page_size, hd]."""
+
+    def __init__(self, k_pages, v_pages) -> None:
+        self.k_pages, self.v_pages = k_pages, v_pages
+
+
+class LatentAttention(PagedAttendMixin, Part):
+    """Attention whose cache holds ONE compressed vector per token, without positions.
+
+    c = RMSNorm(W_dkv x) (plain weight, ``latent_rank`` entries) is all a token leaves in the cache; per
+    head k = W_uk c, v = W_uv c, score = (q . k) * softmax_scale, causal softmax, the head's output times
+    sigmoid(W_g x)_h (one gate per head), then W_o.  A layer with ``own_latent`` false stores nothing: it
+    reads the pages of the run it shares a cache with (``LayerRun.cache_of``) through its own W_uk, W_uv.
+
+    Keys and values are never materialised.  Since q . (W_uk c) = (W_uk^T q) . c and sum_j p_j W_uv c_j =
+    W_uv sum_j p_j c_j, each head's query is carried into the latent space, the attention runs over the
+    latent pages as keys AND values - one shared "kv head" of size latent_rank, which is exactly what the
+    paged attention kernels of this package take (plain, split-K decode, flash-style and tcgen05 prefill) -
+    and the result leaves through W_uv.  Projections of x (q | gate | dkv) are one product."""
+
+    kernel_modules = ("latent",)       # libraries of csrc that this part's kernels live in
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return spec.num_heads, spec.head_dim, int(e["value_dim"]), int(e["latent_rank"]), bool(e.get("own_latent", True))
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        h, d, v, r, own = LatentAttention._dims(spec)
+        slots = {"q": WeightSlot((h * d, hidden_size))}
+        if own:
+            slots["dkv"] = WeightSlot((r, hidden_size))
+            slots["dkv.norm"] = WeightSlot((r,), init="ones")
+        slots.update({"uk": WeightSlot((h * d, r)), "uv": WeightSlot((h * v, r)), "g": WeightSlot((h, hidden_size)),
+                      "o": WeightSlot((hidden_size, h * v))})
+        return slots
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        h, d, v, r, own = self._dims(spec)
+        if h <= 0 or d <= 0 or v <= 0 or not 0 < r <= 256:
+            raise ConfigError(f"latent attention: heads, sizes must be positive and the latent rank at most 256 (got {r})")
+        # what the attention kernels see: h query heads over one shared head of size r
+        self.n_heads, self.n_kv, self.head_dim = h, 1, r
+        self.qk_dim, self.value_dim, self.rank, self.own_latent = d, v, r, own
+        self.window = None
+        self.scale = float(spec.softmax_scale)
+        self.eps = float(spec.extra_dict().get("norm_eps", 1e-6))
+        self.position = part("position", "none")(spec.position, hidden_size, {}, rt)
+        rows = [weights["q"], weights["g"]] + ([weights["dkv"]] if own else [])
+        self.w_in = rt.weight(torch.cat(rows, dim=0))
+        self.latent_gain = rt.gain(weights["dkv.norm"]) if own else None
+        self.w_uk_t = rt.weight(weights["uk"].view(h, d, r).transpose(1, 2))      # [h, r, d]: q -> latent space
+        self.w_uv = rt.weight(weights["uv"].view(h, v, r))                         # [h, v, r]: latent space -> values
+        self.w_o = rt.weight(weights["o"])
+
+    def cache_need(self):
+        return PagedNeed((("latent", (self.rank,)),), None) if self.own_latent else None
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_in, self.w_o)
+
+    adds_into_residual = True
+    graph_safe = "all"
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual=None):
         rt = self.rt
-        common = (self.n_heads, self.n_kv, self.head_dim, rt.page_size, self.window, self.scale)
-        n = q.shape[0]
-        slopes = getattr(self.position, "head_slopes", None)
-        if rt.dtype != torch.bfloat16 or slopes is not None:
-            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)):
-            # the plain kernel takes both; the tensor-core kernels know rotations only
-            ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                  table, *common, head_slopes=slopes)
-            return
-        decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
-        prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM
-        plan = None if ctx.decode_only else ctx.plan_of(self)    # a step of single tokens needs no lists
-        n_dec = n if plan is None else plan.scalars["n_dec"]
-        dec_list = None if plan is None else plan.arrays["dec_tokens"]
-        if n_dec > 0:
-            if decode_ok and rt.balanced_attention(n_dec, self.n_kv, self.head_dim) and n_dec <= ops.DECODE_BALANCED_MAX_ITEMS:
-                # many tokens: their keys dealt evenly over a fixed set of blocks, whatever their lengths
-                scratch = rt.workspace("attention_decode_balanced_partials",
-                                       ops.attention_decode_balanced_scratch(self.n_heads, self.n_kv, self.head_dim), torch.float32)
-                tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
-                ops.attention_decode_balanced(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
-                                              ctx.seq_of_token, table, *common, scratch, tickets,
-                                              warm=rt.warm_attention(self.w_o, ctx))
-            elif decode_ok:
-                splits = ops.decode_splits(n_dec, self.n_kv, self.head_dim, ctx.max_kv_len)
-                scratch = rt.workspace("attention_decode_partials",
-                                       n_dec * self.n_heads * splits * (self.head_dim + 2), torch.float32)
-                tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
-                ops.attention_decode(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
-                                     ctx.seq_of_token, table, *common, splits, scratch, tickets,
-                                     warm=rt.warm_attention(self.w_o, ctx))
-            else:
-                ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                      table, *common, token_list=dec_list)
-        if plan is not None and plan.scalars["n_tiles"] > 0:
-            if prefill_ok:
-                ops.attention_prefill(q, cache.k_pages, cache.v_pages, att, plan.arrays["tile_seq"],
-                                      plan.arrays["tile_row0"], plan.scalars["n_tiles"], ctx.cu_q, ctx.kv_len, table,
-                                      *common)
-            else:
-                ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                      table, *common, token_list=plan.arrays["long_tokens"])
+        n = x.shape[0]
+        h, d, v, r = self.n_heads, self.qk_dim, self.value_dim, self.rank
+        table = ctx.block_tables[cache.group]
+        pages = cache.pages["latent"]                                  # [P, page_size, r]
+        proj = rt.linear(x, self.w_in)                                 # q | gate | dkv
+        if self.own_latent:
+            if not cache.writable:
+                raise ConfigError("latent attention: a layer with a latent of its own needs a cache of its own")
+            ops.latent_norm_write(proj, h * d + h, r, self.latent_gain, self.eps, pages, ctx.positions,
+                                  ctx.seq_of_token, table, rt.page_size)
+        q_latent = rt.heads_linear(proj[:, :h * d], self.w_uk_t)       # [T, h r]
+        mixed = rt.empty(n, h * r)
+        as_kv = pages.view(pages.shape[0], 1, rt.page_size, r)
+        self._attend(q_latent, _KeyValuePages(as_kv, as_kv), mixed, ctx, table)
+        out = rt.heads_linear(mixed, self.w_uv)                        # [T, h v]
+        ops.head_gate(out, proj, h * d, h, v)
+        return rt.linear(out, self.w_o, residual=residual)
 
 
 def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
@@ -209,3 +303,4 @@ def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: in
 
 
 register_part("mixer", "attention", PagedAttention, replace=True)
+register_part("mixer", "latent_attention", LatentAttention, replace=True)

@@ -35,4 +35,20 @@ class RMSNorm(Part):
         return out
 
 
+class ScalarRMSNorm(RMSNorm):
+    """y = x * rsqrt(mean(x^2) + eps) * g with ONE gain g for all coordinates (stored as a tensor without
+    axes).  On the device the gain is spread over the width, so every kernel that takes an RMSNorm - the
+    fused ones included - takes this one unchanged."""
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        return {"weight": WeightSlot((), init="ones")}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        self.eps = float(spec.eps)
+        self.gain = rt.gain(weights["weight"]).reshape(1).expand(hidden_size).contiguous()
+
+
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+register_part("norm", "rmsnorm_scalar", ScalarRMSNorm, replace=True)

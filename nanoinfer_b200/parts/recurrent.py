@@ -1,0 +1,93 @@
+"""Recurrent token mixers: a fixed-size state per request instead of a cache that grows."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..config.model_config import ConfigError
+from ..config.registry import register_part
+from ..kernels import ops
+from .base import Part, StateNeed, WeightSlot
+
+
+class GatedDeltaRule(Part):
+    """The gated delta rule.  Per value head, with a matrix state S [dim, value_dim] in FP32:
+
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+
+    q and k (``num_kv_heads`` heads of ``head_dim``; value head h reads head h / (heads / kv heads)) and
+    v (``num_heads`` heads of ``value_dim``) pass a short causal convolution over time per channel
+    (``conv_taps`` taps, the last one the current token's, no bias) and silu; q and k are then unit
+    vectors per head (1e-6 under the root), q also times head_dim^-1/2.  beta = sigmoid(W_b x), one per
+    head; g = exp(-exp(A_log) softplus(W_a x + dt_bias)), one per head.  Each head's o is divided by its
+    root mean square (``norm_eps``), multiplied by a weight [value_dim] shared by the heads and by
+    silu(W_g x), and leaves through W_o.
+
+    All projections of x are ONE product (rows q | k | v | gate | b | a) whose results stay FP32;
+    everything from there to the gated norm is FP32 on the device.  A request's state is one FP32 vector:
+    S of every head, then the last conv_taps - 1 inputs of every convolved channel.  A step's kernels
+    run exactly once, so the state advances by exactly the step's tokens."""
+
+    kernel_modules = ("delta_rule",)       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = True
+    graph_safe = "all"
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return spec.num_kv_heads, spec.num_heads, spec.head_dim, int(e["value_dim"]), int(e["conv_taps"])
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        g, h, d, v, taps = GatedDeltaRule._dims(spec)
+        return {"q": WeightSlot((g * d, hidden_size)), "q.conv": WeightSlot((g * d, taps)),
+                "k": WeightSlot((g * d, hidden_size)), "k.conv": WeightSlot((g * d, taps)),
+                "v": WeightSlot((h * v, hidden_size)), "v.conv": WeightSlot((h * v, taps)),
+                "b": WeightSlot((h, hidden_size)), "A_log": WeightSlot((h,)), "norm": WeightSlot((v,), init="ones"),
+                "a": WeightSlot((h, hidden_size)), "dt_bias": WeightSlot((h,)),
+                "g": WeightSlot((h * v, hidden_size)), "o": WeightSlot((hidden_size, h * v))}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        g, h, d, v, taps = self._dims(spec)
+        if g <= 0 or h <= 0 or h % g:
+            raise ConfigError("gated delta rule: heads must be a positive multiple of kv_heads")
+        if not 0 < d <= 256:
+            raise ConfigError(f"gated delta rule: a key size of {d} is not supported (1 to 256)")
+        if v <= 0 or taps <= 0:
+            raise ConfigError("gated delta rule: value size and convolution taps must be positive")
+        self.G, self.H, self.D, self.V, self.taps = g, h, d, v, taps
+        self.eps = float(spec.extra_dict().get("norm_eps", 1e-6))
+        self.channels = 2 * g * d + h * v
+        self.w_in = rt.weight(torch.cat([weights[s] for s in ("q", "k", "v", "g", "b", "a")], dim=0))
+        self.w_o = rt.weight(weights["o"])
+        self.conv_w = rt.gain(torch.cat([weights[s] for s in ("q.conv", "k.conv", "v.conv")], dim=0))
+        self.a_log, self.dt_bias = rt.gain(weights["A_log"]), rt.gain(weights["dt_bias"])
+        self.norm_w = rt.gain(weights["norm"])
+
+    def cache_need(self):
+        return StateNeed((self.H * self.D * self.V + (self.taps - 1) * self.channels,), "float32")
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_in, self.w_o)
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual=None):
+        rt = self.rt
+        n = x.shape[0]
+        f32 = torch.float32
+        g, h, d, v = self.G, self.H, self.D, self.V
+        proj = rt.linear(x, self.w_in, out_dtype=f32)
+        qkv = rt.empty(n, self.channels, dtype=f32)
+        beta, decay = rt.empty(n, h, dtype=f32), rt.empty(n, h, dtype=f32)
+        ops.delta_prepare(proj, self.conv_w, self.a_log, self.dt_bias, cache.state, ctx.seq_of_token, ctx.cu_q,
+                          ctx.slots, ctx.n_seqs, g, h, d, v, self.taps, qkv, beta, decay)
+        o = rt.empty(n, h * v, dtype=f32)
+        ops.delta_recurrence(qkv, beta, decay, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, g, h, d, v, o)
+        y = rt.empty(n, h * v)
+        ops.delta_gated_norm(o, proj, self.norm_w, self.eps, g, h, d, v, y)
+        return rt.linear(y, self.w_o, residual=residual)
+
+
+register_part("mixer", "gated_delta", GatedDeltaRule, replace=True)

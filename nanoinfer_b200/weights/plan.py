@@ -39,10 +39,15 @@ def tensor_plan(config: ModelConfig) -> List[PlannedTensor]:
             registry.part("norm", layer.mixer_norm.kind).weight_slots(layer.mixer_norm, d))
         add(("layer", i, "mixer"),
             registry.part("mixer", layer.mixer.kind).weight_slots(layer.mixer, d))
-        add(("layer", i, "ffn_norm"),
-            registry.part("norm", layer.ffn_norm.kind).weight_slots(layer.ffn_norm, d))
-        add(("layer", i, "feed_forward"),
-            registry.part("feed_forward", layer.feed_forward.kind).weight_slots(layer.feed_forward, d))
+        if layer.ffn_norm is not None:
+            add(("layer", i, "ffn_norm"),
+                registry.part("norm", layer.ffn_norm.kind).weight_slots(layer.ffn_norm, d))
+        if layer.feed_forward is not None:
+            add(("layer", i, "feed_forward"),
+                registry.part("feed_forward", layer.feed_forward.kind).weight_slots(layer.feed_forward, d))
+        block = registry.part("arrangement", layer.arrangement)
+        if hasattr(block, "weight_slots"):                    # weights of the arrangement itself
+            add(("layer", i, "block"), block.weight_slots(layer, d))
     add(("final_norm",),
         registry.part("norm", config.final_norm.kind).weight_slots(config.final_norm, d))
     head = config.head_spec()
