@@ -1,0 +1,337 @@
+"""Runevik on the GPU against the plain implementation (tests/plain_runevik.py): every mechanism alone, then
+whole models replayed under four ways of cutting the same requests - in 32-bit and in bfloat16 - and greedy
+generation through the engine.  The models are small, of other sizes than any real one, with weights tuned
+so that a lost key, a lost state or a shifted convolution tap moves the logits far beyond rounding."""
+import copy
+
+import pytest
+import torch
+
+import replay_util as ru
+import tiny_runevik as tr
+from helpers import load_plain, random_tokens
+from plain_runevik import (PlainRunevik, delta_mixer, delta_state, gelu_tanh, over_rms, sinusoid)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+CUTS = {"whole": ru.whole, "tail": ru.tail_by_token, "ragged": ru.ragged, "mixed": ru.mixed}
+LENGTHS = {"r1": [1, 2, 17, 33, 70, 130, 49], "r2": [3, 16, 64, 150, 31, 97], "r3": [2, 48, 129, 15, 80]}
+RAW = {"r1": tr.R1, "r2": tr.R2, "r3": tr.R3}
+
+
+def _keep_state(tensors):
+    """Decays close to one, so that what a delta layer wrote hundreds of tokens ago still counts."""
+    for name, t in tensors.items():
+        if name.endswith("mix.A_log"):
+            t.fill_(-4.0)
+        if name.endswith(".norm1") or name == "final.norm":
+            t.fill_(1.25)
+        if name.endswith("mix.norm") or name.endswith("side.norm") or name.endswith("dkv.norm"):
+            t.copy_((1.0 + 0.3 * torch.randn(t.shape, generator=torch.Generator().manual_seed(t.numel()))).to(t.dtype))
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """{key: (folder, config dictionary, requests, plain logits per request)}"""
+    root = tmp_path_factory.mktemp("runevik")
+    out = {}
+    for seed, (key, raw) in enumerate(RAW.items()):
+        d = str(root / key)
+        tr.write_model(d, raw, seed + 11, tune=_keep_state)
+        cfg, w = load_plain(d)
+        plain = PlainRunevik(cfg, w)
+        reqs = {f"q{i}": random_tokens(raw["vocab"], n, 31 * seed + i) for i, n in enumerate(LENGTHS[key])}
+        want = {rid: plain.run(toks, plain.new_state())[0].float() for rid, toks in reqs.items()}
+        out[key] = (d, cfg, reqs, want)
+    return out
+
+
+# bfloat16 bounds of the whole-model replays, fixed before the first run that used them: twice those of the
+# Llama replays (ru.compare), since a layer of this design rounds more often on the way to the stream - three
+# normed sums (mixer output, feed-forward activation, token input) whose direction carries every rounding of
+# their inputs at full weight.  A lost key or state moves these models' logits by ten times as much (the
+# far-token tests, which keep the tighter bounds, show it).
+BF16_MAX_REL, BF16_RMS_REL = 0.10, 0.03
+
+
+def _compare(got, want, dtype, label):
+    if dtype == "float32":
+        return ru.compare(got, want, dtype, label)
+    assert got
+    for (rid, pos), row in got.items():
+        ref = want[rid][pos]
+        err = (row - ref).abs()
+        assert err.max().item() <= BF16_MAX_REL * ref.abs().max().item(), f"{label} {rid} position {pos}: max error {err.max().item():.4g}"
+        assert err.pow(2).mean().sqrt().item() <= BF16_RMS_REL * ref.pow(2).mean().sqrt().item(), \
+            f"{label} {rid} position {pos}: rms error {err.pow(2).mean().sqrt().item():.4g}"
+
+
+def _runner(model_dir, dtype, steps, page=16, max_requests=4, **kw):
+    from nanoinfer_b200.config import load_config
+    from nanoinfer_b200.engine import ModelRunner
+    from nanoinfer_b200.weights import load_weights
+    cfg = load_config(model_dir)
+    num_pages = max(1, ru.max_live_tokens(steps, 64) // page)
+    return ModelRunner(cfg, load_weights(model_dir, cfg), dtype=dtype, page_size=page, num_pages=num_pages,
+                       max_requests=max_requests, **kw)
+
+
+# ---- mechanisms alone ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rowwise_kernels(dtype):
+    from nanoinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(5)
+    tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+    # embedding + sinusoid, odd width, positions far out
+    table = torch.randn(50, 37, generator=g).to(dtype)
+    tokens = torch.tensor([3, 49, 0, 7], dtype=torch.int32)
+    pos = torch.tensor([0, 1, 511, 1290], dtype=torch.int32)
+    i = torch.arange(19, dtype=torch.float64)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2 * i / 37).float()
+    out = torch.empty(4, 37, device=DEV)
+    ops.embedding_sinusoid(tokens.to(DEV), pos.to(DEV), table.to(DEV), inv.to(DEV), out)
+    want = table.double()[tokens.long()] + sinusoid(pos.tolist(), 37, torch.float64)
+    torch.testing.assert_close(out.cpu().double(), want, rtol=0, atol=3e-4)     # FP32 angles at position 1290
+    # PolyNorm, a width that is no multiple of the block
+    z = (torch.randn(5, 203, generator=g) * 1.7).to(dtype)
+    coef = torch.tensor([0.7, -0.4, 0.25, 0.1])
+    act = torch.empty(5, 203, dtype=dtype, device=DEV)
+    ops.polynorm(z.to(DEV), coef.to(DEV), 1e-5, act)
+    zd = z.double()
+    want = 0.7 * over_rms(zd, 1e-5) - 0.4 * over_rms(zd ** 2, 1e-5) + 0.25 * over_rms(zd ** 3, 1e-5) + 0.1
+    torch.testing.assert_close(act.cpu().double(), want, **tol)
+    # normed addition into the stream
+    h = torch.randn(5, 203, generator=g)
+    y = (torch.randn(5, 203, generator=g) * 3).to(dtype)
+    wt = torch.rand(203, generator=g) + 0.5
+    hd = h.clone().to(DEV)
+    ops.add_normed(hd, y.to(DEV), wt.to(DEV), 1e-5)
+    torch.testing.assert_close(hd.cpu().double(), h.double() + over_rms(y.double(), 1e-5) * wt.double(), rtol=2e-5, atol=2e-5)
+    # gelu gate times a table row
+    gate = torch.randn(4, 6, generator=g).to(dtype)
+    tab = torch.randn(50, 30, generator=g).to(dtype)
+    out = torch.empty(4, 6, dtype=dtype, device=DEV)
+    ops.gelu_table_gate(gate.to(DEV), tokens.to(DEV), tab.to(DEV), 12, out)
+    torch.testing.assert_close(out.cpu().double(), gelu_tanh(gate.double()) * tab.double()[tokens.long(), 12:18], **tol)
+
+
+@pytest.mark.parametrize("G, H, D, V, taps", [(1, 2, 24, 40, 3), (2, 2, 160, 33, 1), (2, 4, 64, 64, 4), (1, 1, 8, 8, 6)])
+def test_delta_kernels_alone(G, H, D, V, taps):
+    """Two requests whose tokens arrive in three steps of unequal portions (one of them shorter than the
+    convolution's history), in slots that are not in order; the plain mixer gets the same inputs through
+    projections that merely select columns."""
+    from nanoinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(G + 10 * H + D)
+    C, N = 2 * G * D + H * V, 2 * G * D + 2 * H * V + 2 * H
+    lens = {"a": 11, "b": 7}
+    inputs = {k: torch.randn(n, N, generator=g) for k, n in lens.items()}
+    conv_w = torch.randn(C, taps, generator=g) * 0.6
+    a_log, dt_bias = torch.randn(H, generator=g) - 2.0, torch.randn(H, generator=g)
+    norm_w = torch.rand(V, generator=g) + 0.5
+    state = torch.full((5, H * D * V + (taps - 1) * C), 7.0, device=DEV)
+    slot = {"a": 3, "b": 1}
+    for s in slot.values():
+        state[s].zero_()
+    got = {k: [] for k in lens}
+    fed = {k: 0 for k in lens}
+    for step in ({"a": 5, "b": 1}, {"b": 4, "a": 1}, {"a": 5, "b": 2}):
+        ids = list(step)
+        proj = torch.cat([inputs[k][fed[k]:fed[k] + step[k]] for k in ids]).to(DEV)
+        n = proj.shape[0]
+        cu = torch.tensor([0] + list(torch.tensor([step[k] for k in ids]).cumsum(0)), dtype=torch.int32, device=DEV)
+        seq = torch.repeat_interleave(torch.arange(len(ids)), torch.tensor([step[k] for k in ids])).int().to(DEV)
+        slots = torch.tensor([slot[k] for k in ids], dtype=torch.int32, device=DEV)
+        qkv = torch.empty(n, C, device=DEV)
+        beta, decay = torch.empty(n, H, device=DEV), torch.empty(n, H, device=DEV)
+        ops.delta_prepare(proj, conv_w.to(DEV), a_log.to(DEV), dt_bias.to(DEV), state, seq, cu, slots, len(ids), G, H, D, V,
+                          taps, qkv, beta, decay)
+        o = torch.empty(n, H * V, device=DEV)
+        ops.delta_recurrence(qkv, beta, decay, state, cu, slots, len(ids), G, H, D, V, o)
+        y = torch.empty(n, H * V, device=DEV)
+        ops.delta_gated_norm(o, proj, norm_w.to(DEV), 1e-5, G, H, D, V, y)
+        at = 0
+        for k in ids:
+            got[k].append(y[at:at + step[k]].cpu())
+            at += step[k]
+            fed[k] += step[k]
+    assert bool((state[0] == 7.0).all()) and bool((state[2] == 7.0).all()) and bool((state[4] == 7.0).all())
+    eye = torch.eye(N, dtype=torch.float64)
+    cols = {"q": (0, G * D), "k": (G * D, 2 * G * D), "v": (2 * G * D, C), "g": (C, C + H * V), "b": (C + H * V, C + H * V + H),
+            "a": (C + H * V + H, N)}
+    w = {k: eye[a:b] for k, (a, b) in cols.items()}
+    w.update({"q.conv": conv_w[:G * D].double(), "k.conv": conv_w[G * D:2 * G * D].double(), "v.conv": conv_w[2 * G * D:].double(),
+              "A_log": a_log.double(), "dt_bias": dt_bias.double(), "norm": norm_w.double(), "o": torch.eye(H * V, dtype=torch.float64)})
+    m = {"heads": H, "kv_heads": G, "dim": D, "vdim": V, "conv": taps}
+    for k in lens:
+        want = delta_mixer(inputs[k].double(), w, m, 1e-5, delta_state(m, torch.float64))
+        torch.testing.assert_close(torch.cat(got[k]).double(), want, rtol=2e-4, atol=2e-5)
+
+
+def _one_layer(layer, width=64, vocab=120, side=None):
+    raw = {"architecture": "Runevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": [layer]}
+    if side:
+        raw["token_side"] = {"dim": side}
+    return raw
+
+
+def _far_token_matters(tmp_path, raw, tune, dtype, n=300, far=3, last=2):
+    """A prompt whose last token (``last``) looks for token 2, which stands at position ``far`` and nowhere else;
+    putting token 3 there instead must move the plain logits at the end by much, and the engine must follow
+    both prompts."""
+    from nanoinfer_b200.engine import StepEntry
+    d = str(tmp_path / "m")
+    tr.write_model(d, raw, 7, tune=tune)
+    cfg, w = load_plain(d)
+    plain = PlainRunevik(cfg, w)
+    base = [5 + (i % 90) for i in range(n)]
+    base[far], base[-1] = 2, last
+    other = list(base)
+    other[far] = 3
+    want = {k: plain.run(t, plain.new_state())[0][-1].float() for k, t in (("same", base), ("other", other))}
+    moved = (want["same"] - want["other"]).abs().max().item()
+    assert moved > 0.1 * want["same"].abs().max().item(), "the test's weights do not make the far token count"
+    steps = ru.whole({"same": base, "other": other})
+    runner = _runner(d, dtype, steps, max_requests=2)
+    for k, toks in (("same", base), ("other", other)):
+        # most of the prompt at once, then portions that end at and just after page borders, then single tokens
+        cuts = [0, 250, 256, 257, 272, 290] + list(range(291, n + 1))
+        for a, b in zip(cuts, cuts[1:]):
+            logits = runner.step([StepEntry(k, toks[a:b], [b - a - 1])])
+        runner.end(k)
+        ru.compare({(k, n - 1): logits[0].cpu()}, {k: {n - 1: want[k]}}, dtype, label=f"far token, {k}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_latent_attention_finds_a_far_key(tmp_path, dtype):
+    """Queries that look for their own token: q = s * W_uk W_dkv, so the score of a key is large where the key's
+    token equals the query's; token identity dominates the embedding."""
+    def tune(t):
+        t["embed"].mul_(4.0)
+        uk = t["l0.mix.uk"].float()
+        t["l0.mix.q"].copy_((10.0 * uk @ t["l0.mix.dkv"].float()).to(t["l0.mix.q"].dtype))
+        t["l0.mix.g"].zero_()
+        t["l0.mix.o"].mul_(12.0)
+    raw = _one_layer(tr.latent(2, 32, 24, 64, 0.5, 0))
+    _far_token_matters(tmp_path, raw, tune, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_delta_state_keeps_a_far_token(tmp_path, dtype):
+    """Decays of nearly one.  Tokens 2 and 4 have a spike in one coordinate of their embedding that no other token
+    has, token 3 in another; the key (and read-out query) projections turn each spike into a key of its own, so
+    what token 2 wrote at position 3 stays untouched by the 295 tokens that follow and is read by token 4 at the
+    end - unless token 3 stood there, which writes elsewhere."""
+    def tune(t):
+        e = t["embed"]
+        e.mul_(4.0)
+        e[:, 60] = 0
+        e[:, 62] = 0
+        e[2, 60] = e[4, 60] = e[3, 62] = 30.0
+        k = t["l0.mix.k"]
+        k[:, 60] = 0
+        k[:, 62] = 0
+        k[0] = 0
+        k[1] = 0
+        k[0, 60] = k[1, 62] = 1.0
+        t["l0.mix.v"][:, 60] = 0
+        t["l0.mix.v"][:, 62] = 0
+        t["l0.mix.v"].mul_(5.0)
+        t["l0.mix.q"].copy_(k)
+        t["l0.mix.q.conv"].copy_(t["l0.mix.k.conv"])
+        for name in ("l0.mix.q.conv", "l0.mix.k.conv", "l0.mix.v.conv"):
+            t[name][:, :-1].mul_(0.1)                # mostly the current token
+            t[name][:, -1] = t[name][:, -1].abs() + 0.5
+        t["l0.mix.A_log"].fill_(-7.0)
+        t["l0.mix.o"].mul_(6.0)
+        t["l0.mix.g"].mul_(10.0)
+    raw = _one_layer(tr.delta(2, 1, 64, 24, 3, 0))
+    _far_token_matters(tmp_path, raw, tune, dtype, last=4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_token_input_and_polynorm_alone(tmp_path, dtype):
+    """One layer whose mixer is silenced (zero output projection): what is left is the feed-forward and the
+    token input; with the feed-forward's output silenced too, only the token input."""
+    for silence in (("l0.mix.o",), ("l0.mix.o", "l0.mlp.down")):
+        def tune(t, silence=silence):
+            for name in silence:
+                t[name].zero_()
+        raw = _one_layer(tr.delta(1, 1, 16, 16, 2, 72), width=48, side=12)
+        d = str(tmp_path / ("m" + str(len(silence))))
+        tr.write_model(d, raw, 9, tune=tune)
+        cfg, w = load_plain(d)
+        plain = PlainRunevik(cfg, w)
+        reqs = {"a": random_tokens(120, 19, 1), "b": random_tokens(120, 2, 2)}
+        want = {rid: plain.run(toks, plain.new_state())[0].float() for rid, toks in reqs.items()}
+        steps = ru.ragged(reqs, sizes=(5, 2, 7))
+        ru.compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, label="token input")
+
+
+# ---- whole models, cut in four ways ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", list(RAW))
+def test_replay_matches_plain(models, key, dtype, cut):
+    d, cfg, reqs, want = models[key]
+    steps = CUTS[cut](reqs)
+    runner = _runner(d, dtype, steps)
+    got = ru.run_trace(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _compare(got, want, dtype, label=f"{key} {cut}")
+    runner.cache.check_consistency()
+    assert runner.cache.num_free_slots == 4
+
+
+@pytest.mark.parametrize("key", list(RAW))
+def test_float32_does_not_depend_on_the_cut(models, key):
+    """In 32-bit every cut gives the same bits: portions, batches, pages and slots only move data."""
+    d, cfg, reqs, want = models[key]
+    ref = None
+    for cut in CUTS:
+        steps = CUTS[cut](reqs)
+        got = ru.run_trace(_runner(d, "float32", steps), steps)
+        if ref is None:
+            ref = got
+        else:
+            for k in ref:
+                assert torch.equal(ref[k], got[k]), f"{key}: {cut} differs from whole at {k}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_with_replayed_graphs(models, dtype):
+    """Most of a request token by token (the steps are captured and replayed from the third on), a second request
+    decoding beside it from the middle on."""
+    d, cfg, reqs, want = models["r2"]
+    reqs = {k: reqs[k] for k in ("q3", "q5")}
+    steps = ru.tail_by_token({"q3": reqs["q3"]}, tail=140)
+    join = ru.tail_by_token({"q5": reqs["q5"]}, tail=60)
+    for i, st in enumerate(join):                       # q5 runs beside q3's single tokens
+        steps[30 + i]["entries"] += st["entries"]
+        steps[30 + i]["end"] += st["end"]
+    runner = _runner(d, dtype, steps)
+    _compare(ru.run_trace(runner, steps), want, dtype, label="long decoding")
+    assert runner._graphs, "no step of single tokens was captured"
+
+
+def test_greedy_generation_through_the_engine(models):
+    """Engine.generate (scheduler, chunked prompts, sampling kernels) against greedy decoding of the plain model."""
+    from nanoinfer_b200 import Engine, SamplingParams
+    d, cfg, reqs, want = models["r1"]
+    raw_cfg, w = load_plain(d)
+    plain = PlainRunevik(raw_cfg, w)
+    prompts = [reqs["q2"], reqs["q3"][:20], reqs["q1"]]
+    engine = Engine.from_model_dir(d, dtype="float32", block_size=16, num_cache_blocks=64, max_batch_size=4,
+                                   max_sequences=4, prefill_chunk_size=12)
+    out = engine.generate(prompts, max_new_tokens=12, sampling_params=SamplingParams.greedy())
+    for prompt, got in zip(prompts, out):
+        st = plain.new_state()
+        logits = plain.run(prompt, st)[0][-1]
+        for t in got:
+            top2 = torch.topk(logits, 2).values
+            if int(torch.argmax(logits)) != t:
+                assert (top2[0] - logits[t]).item() < 1e-4, "the engine chose a token that the plain model ranks lower"
+            logits = plain.run([t], st)[0][-1]
+        assert len(got) == 12
