@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine at the Llama 3.2 1B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 16] [--impl ours|reference]
+    python bench.py --design runevik [--sizes w1024,w2048]     (another design beside the Llama model of equal size)
 
 A "step" is one decode step of the whole batch.  Every request starts at a context of 2,048
 tokens and decodes W + K tokens (by default to 4,096).  Prints ONE JSON line:
@@ -370,6 +371,111 @@ def run_serving(args):
     return 0
 
 
+# Layer sizes for --design: a Runevik model and the Llama model of the same width, feed-forward width, layer
+# count and vocabulary (the closest model the engine had before).  Three delta layers, then a latent-attention
+# layer; every second latent layer reads the latents of the one before it.
+DESIGN_SIZES = {
+    "w1024": {"width": 1024, "ff": 4096, "layers": 8, "vocab": 32000, "heads": 8, "kv_heads": 4, "side": 128},
+    "w2048": {"width": 2048, "ff": 8192, "layers": 16, "vocab": 32000, "heads": 16, "kv_heads": 8, "side": 256},
+    "w3072": {"width": 3072, "ff": 8192, "layers": 16, "vocab": 32000, "heads": 16, "kv_heads": 8, "side": 256},
+}
+
+
+def runevik_config(z):
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    layers, last_own = [], None
+    for i in range(z["layers"]):
+        if i % 4 == 3:
+            m = {"heads": z["heads"], "dim": 128, "vdim": 128, "kv_rank": 128, "scale": 128 ** -0.5}
+            if last_own is not None:
+                m["kv_from"], last_own = last_own, None
+            else:
+                last_own = i
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+        else:
+            layers.append({"type": "delta", "mlp": mlp,
+                           "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "conv": 4}})
+    return {"architecture": "Runevik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "token_side": {"dim": z["side"]}, "layers": layers}
+
+
+def llama_config(z):
+    return {"architectures": ["LlamaForCausalLM"], "hidden_size": z["width"], "intermediate_size": z["ff"],
+            "num_hidden_layers": z["layers"], "num_attention_heads": z["width"] // 128, "num_key_value_heads": z["kv_heads"],
+            "head_dim": 128, "vocab_size": z["vocab"], "max_position_embeddings": 131072, "rms_norm_eps": 1e-5,
+            "rope_theta": 500000.0, "rope_scaling": None, "tie_word_embeddings": False, "hidden_act": "silu"}
+
+
+def run_design(args):
+    """Prefill and decode throughput of the Runevik design beside the Llama model of equal size (random weights)."""
+    import torch
+    from nanoinfer_b200.config import config_from_dict
+    from nanoinfer_b200.engine import ModelRunner, StepEntry
+    from nanoinfer_b200.kernels import ops
+
+    device = "cuda:0"
+    torch.cuda.set_device(0)
+    K, W, B = args.steps, max(3, args.warmup), args.batch or 8
+    ctx0, T = args.context, args.prefill_tokens
+    page = 16
+    gen = torch.Generator().manual_seed(0)
+    clocks = ClockSampler()
+    clocks.start()
+    results = {}
+    for size in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
+        z = DESIGN_SIZES[size]
+        row = {}
+        for name, raw in (("runevik", runevik_config(z)), ("llama", llama_config(z))):
+            config = config_from_dict(raw)
+            weights = device_weights(config, 0, device)
+            per_request = -(-(max(ctx0 + W + K + 2, T)) // page)
+            runner = ModelRunner(config, weights, dtype="bfloat16", page_size=page, num_pages=(B + 1) * per_request,
+                                 max_requests=B + 1, max_tokens_per_request=per_request * page, device=device)
+            del weights
+
+            def prompt(n):
+                return torch.randint(0, z["vocab"], (n,), generator=gen).tolist()
+
+            def timed(fn):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b)
+
+            ms = []
+            for i in range(8):                     # the step shape is replayed from a graph from its fourth time on
+                p = prompt(T)
+                ms.append(timed(lambda: runner.step([StepEntry(("p", i), p, [T - 1])])))
+                runner.end(("p", i))
+            prefill_ms = sorted(ms[5:])[1]
+            reqs = [("d", i) for i in range(B)]
+            last = []
+            for r in reqs:
+                logits = runner.step([StepEntry(r, prompt(ctx0), [ctx0 - 1])])
+                last.append(int(torch.argmax(logits[0])))
+            toks = runner.greedy_decode_on_device(reqs, last, W)
+            launches = runner._decode_graph(B).greedy_launches
+            decode_ms = timed(lambda: runner.greedy_decode_on_device(reqs, toks[-1].tolist(), K)) / K
+            ops.check_device_errors(device)
+            row[name] = {"prefill_tok_s": round(T / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                         "decode_tok_s": round(B / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+                         "kernels_per_decode_step": launches}
+            del runner
+            torch.cuda.empty_cache()
+        row["sizes"] = z
+        results[size] = row
+    out = {"metric": "design_prefill_and_decode_tokens_per_second", "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+           "dtype": "bf16", "data": "synthetic", "impl": "ours", "higher_is_better": True,
+           "config": {"batch": B, "start_context": ctx0, "prefill_tokens": T, "kv_page_size": page,
+                      "weights": "random N(0,0.02) bf16", "l2_policy": "inputs larger than L2 (weights and states per step)"},
+           "clocks": clocks.stop(), "designs": results}
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -382,6 +488,9 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode"] + sorted(WORKLOADS),
                     help="decode: the timed decode step (the published line); the others serve a set of requests")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")
+    ap.add_argument("--design", default=None, choices=["runevik"],
+                    help="prefill and decode throughput of this design beside the Llama model of equal size, at a few sizes")
+    ap.add_argument("--sizes", default=None, help="--design: which of " + ",".join(DESIGN_SIZES) + " (default: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
     args = ap.parse_args()
@@ -395,6 +504,10 @@ def main():
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.design is not None:
+        if args.steps == 2024:
+            args.steps = 256                    # a few sizes, two models each: a shorter run per point
+        return run_design(args)
     if args.workload != "decode":
         return run_serving(args)
     args.shape = args.shape or "llama-3.2-1b"

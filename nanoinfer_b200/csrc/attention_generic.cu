@@ -16,9 +16,9 @@
 // divides by (sum + 1e-6); this kernel divides by the sum.
 #include "common.cuh"
 
-#define ATT_MAX_REGS 8  // head_dim <= 256
-
-template <typename T>
+// Registers per lane for a head: 8 take head sizes up to 256; a second instance with 16 takes up to 512
+// (a compressed cache row can be that wide) and leaves the first one as it was.
+template <typename T, int ATT_MAX_REGS>
 __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                                          const T* __restrict__ v_pages, T* __restrict__ out,
                                          const int* __restrict__ token_list,
@@ -92,19 +92,25 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
     if (n_tokens <= 0) return NI_OK;
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0)
         return NI_ERR_BAD_ARGUMENT;
-    if (head_dim > 32 * ATT_MAX_REGS) return NI_ERR_UNSUPPORTED_SIZE;
+    if (head_dim > 32 * 16) return NI_ERR_UNSUPPORTED_SIZE;
     const int warps = 4;
     const long long items = (long long)n_tokens * n_q_heads;
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
-#define LAUNCH(T)                                                                                   \
-    attention_generic_kernel<T><<<(int)blocks, warps * 32, 0, stream>>>(                            \
+#define LAUNCH_R(T, R)                                                                              \
+    attention_generic_kernel<T, R><<<(int)blocks, warps * 32, 0, stream>>>(                         \
         (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_list, positions,         \
         seq_of_token,                                                                               \
         block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes)
+#define LAUNCH(T)                          \
+    do {                                   \
+        if (head_dim <= 256) LAUNCH_R(T, 8); \
+        else LAUNCH_R(T, 16);              \
+    } while (0)
     if (dtype == NI_DTYPE_F32) LAUNCH(float);
     else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);
     else return NI_ERR_BAD_ARGUMENT;
 #undef LAUNCH
+#undef LAUNCH_R
     NI_RETURN_LAUNCH_STATUS();
 }

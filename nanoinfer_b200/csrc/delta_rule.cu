@@ -14,7 +14,7 @@
 // Four kernels, all FP32 inside:
 //   delta_prepare      per token: convolution + silu, unit norms, beta, decay
 //   delta_history      per request: the new last taps-1 inputs (after delta_prepare has read the old)
-//   delta_recurrence   per (request, head, 32 value columns): its tokens one after the other
+//   delta_recurrence   per (request, head, a few value columns): its tokens one after the other
 //   delta_gated_norm   per token and head: o / rms(o) * weight * silu(gate)
 // Prompt portions and single tokens are the same case; a token's result depends only on its own
 // request's state and tokens, in a fixed order of operations, however the step is cut.
@@ -50,22 +50,30 @@ __device__ __forceinline__ float dr_conv(const float* __restrict__ proj, const f
     return dr_silu(acc);
 }
 
-// qkv [T, C]: q (unit, times D^-1/2), k (unit), v after convolution and silu; beta, decay [T, H].
-__global__ void delta_prepare_kernel(const float* __restrict__ proj, const float* __restrict__ conv_w,
-                                     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
-                                     const float* __restrict__ state, long long state_stride,
-                                     const int* __restrict__ seq_of_token, const int* __restrict__ cu_q,
-                                     const int* __restrict__ slots, DeltaDims dm, float* __restrict__ qkv,
-                                     float* __restrict__ beta, float* __restrict__ decay) {
+// qkv [T, C]: q (unit, times D^-1/2), k (unit), v after convolution and silu; gates [T, H, 2]: decay, beta.
+// One warp per unit of work of a token: a q or k head (unit norm over its D channels), or 128 channels of v;
+// the first warp of a token also computes beta and decay.  grid = (tokens, units / warps per block).
+#define DP_WARPS 4
+#define DP_VCHUNK 128
+__global__ void __launch_bounds__(DP_WARPS * 32)
+delta_prepare_kernel(const float* __restrict__ proj, const float* __restrict__ conv_w,
+                     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                     const float* __restrict__ state, long long state_stride,
+                     const int* __restrict__ seq_of_token, const int* __restrict__ cu_q,
+                     const int* __restrict__ slots, DeltaDims dm, float* __restrict__ qkv,
+                     float* __restrict__ gates) {
     const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.y * DP_WARPS + (threadIdx.x >> 5);
+    const int C = dm.C(), HV = dm.H * dm.V;
+    const int n_units = 2 * dm.G + (HV + DP_VCHUNK - 1) / DP_VCHUNK;
+    if (unit >= n_units) return;
     const int seq = seq_of_token[t];
     const int in_portion = t - cu_q[seq];
     const float* hist = state + (size_t)slots[seq] * state_stride + dm.hist_off();
-    const int C = dm.C(), lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     float* out = qkv + (size_t)t * C;
-    // q and k heads: one warp per head, unit norm over its D channels
-    for (int u = warp; u < 2 * dm.G; u += nwarps) {
-        const int c0 = u * dm.D;
+    if (unit < 2 * dm.G) {
+        const int c0 = unit * dm.D;
         float ss = 0.f;
         for (int i = lane; i < dm.D; i += 32) {
             const float y = dr_conv(proj, conv_w, hist, dm, t, in_portion, c0 + i);
@@ -74,15 +82,19 @@ __global__ void delta_prepare_kernel(const float* __restrict__ proj, const float
         }
         ss = ni_warp_sum(ss);
         float r = 1.0f / sqrtf(ss + 1e-6f);
-        if (u < dm.G) r *= 1.0f / sqrtf((float)dm.D);
+        if (unit < dm.G) r *= 1.0f / sqrtf((float)dm.D);
         for (int i = lane; i < dm.D; i += 32) out[c0 + i] *= r;   // each lane rescales what it wrote itself
+    } else {
+        const int c0 = 2 * dm.G * dm.D + (unit - 2 * dm.G) * DP_VCHUNK;
+        for (int c = c0 + lane; c < c0 + DP_VCHUNK && c < C; c += 32)
+            out[c] = dr_conv(proj, conv_w, hist, dm, t, in_portion, c);
     }
-    for (int c = 2 * dm.G * dm.D + threadIdx.x; c < C; c += blockDim.x)
-        out[c] = dr_conv(proj, conv_w, hist, dm, t, in_portion, c);
-    for (int h = threadIdx.x; h < dm.H; h += blockDim.x) {
+    if (unit == 0) {
         const float* row = proj + (size_t)t * dm.ld;
-        beta[(size_t)t * dm.H + h] = dr_sigmoid(row[dm.b_off() + h]);
-        decay[(size_t)t * dm.H + h] = expf(-expf(a_log[h]) * dr_softplus(row[dm.a_off() + h] + dt_bias[h]));
+        for (int h = lane; h < dm.H; h += 32) {
+            gates[((size_t)t * dm.H + h) * 2] = expf(-expf(a_log[h]) * dr_softplus(row[dm.a_off() + h] + dt_bias[h]));
+            gates[((size_t)t * dm.H + h) * 2 + 1] = dr_sigmoid(row[dm.b_off() + h]);
+        }
     }
 }
 
@@ -102,83 +114,152 @@ __global__ void delta_history_kernel(const float* __restrict__ proj, float* __re
     }
 }
 
-// One warp per (request, head, 32 value columns): lane = value column, the column of S in registers.
-template <int DMAX>
+// One warp per (request, head, a few value columns).  The rows of a column of S are cut into chunks of 8;
+// a lane keeps CHUNKS of them in registers and RG lanes share a column, so S^T k and S^T q are sums inside a
+// lane followed by log2(RG) shuffles.  The order of every sum is fixed by the chunk numbers alone (8 rows in
+// four interleaved chains, then a binary tree over the chunk index from its lowest bit up), so the two
+// layouts launched below - few lanes per column for single tokens, whose cost is reading and writing S in
+// whole 32-byte sectors, and many lanes per column for long portions, whose cost is the chain of dependent
+// operations per token - give the same bits.  Lanes of one row group sit side by side and read neighbouring
+// columns.  No block barrier.  What a token brings (k, q, the warp's values, decay, beta) travels through a
+// ring of tokens in shared memory, filled by asynchronous copies that run ahead of the arithmetic.
+#define DR_MAX_STAGES 8
+
+__device__ __forceinline__ void dr_copy4(float* dst_smem, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_copy8(float* dst_smem, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_copy16(float* dst_smem, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int CHUNKS, int RG>
 __global__ void __launch_bounds__(32)
-delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
+delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
                         float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ slots, DeltaDims dm, float* __restrict__ out) {
-    __shared__ __align__(16) float ks[2][DMAX];
-    __shared__ __align__(16) float qs[2][DMAX];
-    const int lane = threadIdx.x, h = blockIdx.y, seq = blockIdx.z;
-    const int col = blockIdx.x * 32 + lane;
+    constexpr int ROWS = 8 * CHUNKS, COLS = 32 / RG, DP = ROWS * RG;   // rows per lane; columns per warp; D rounded up
+    constexpr int STAGE = 2 * DP + 12;                     // k | q | v of the warp's columns (up to 8) | decay, beta, -, -
+    constexpr int STAGES = DP >= 1024 ? 4 : DR_MAX_STAGES;
+    __shared__ __align__(16) float ring[STAGES][STAGE];
+    const int lane = threadIdx.x, rg = lane / COLS, cl = lane % COLS;
+    const int h = blockIdx.y, seq = blockIdx.z;
+    const int col = blockIdx.x * COLS + cl;
     const bool live = col < dm.V;
-    const int D = dm.D, C = dm.C();
+    const int D = dm.D, C = dm.C(), row0 = rg * ROWS;
     const int g = h / (dm.H / dm.G);
     const int first = cu_q[seq], last = cu_q[seq + 1];
     if (first >= last) return;
+    const bool wide = (D % 4 == 0) && (C % 4 == 0);        // rows of k and q start on 16-byte boundaries
+    for (int st = 0; st < STAGES; ++st) {                  // entries that no copy ever writes
+        for (int i = lane; i < DP; i += 32)
+            if (i >= D) ring[st][i] = ring[st][DP + i] = 0.f;
+        if (lane < COLS && !live) ring[st][2 * DP + lane] = 0.f;
+    }
+    // Each lane's sources of the next token to fetch, advanced by a row per token; its place in the ring likewise.
+    const float* row = qkv + (size_t)first * C;
+    const float* k_src = row + (dm.G + g) * D + (wide ? 4 * lane : lane);
+    const float* q_src = row + g * D + (wide ? 4 * lane : lane);
+    const float* v_src = row + 2 * dm.G * D + h * dm.V + col;
+    const float* g_src = gates + ((size_t)first * dm.H + h) * 2;
+    int fetch_t = first, fetch_stage = 0;
+    auto fetch = [&]() {                                   // the next token into its stage (nothing past the portion)
+        if (fetch_t < last) {
+            float* sg = ring[fetch_stage];
+            if (wide) {
+#pragma unroll
+                for (int m = 0; m < (DP + 127) / 128; ++m)
+                    if (4 * lane + 128 * m < D) {
+                        dr_copy16(sg + 4 * lane + 128 * m, k_src + 128 * m);
+                        dr_copy16(sg + DP + 4 * lane + 128 * m, q_src + 128 * m);
+                    }
+            } else {
+#pragma unroll
+                for (int m = 0; m < DP / 32; ++m)
+                    if (lane + 32 * m < D) {
+                        dr_copy4(sg + lane + 32 * m, k_src + 32 * m);
+                        dr_copy4(sg + DP + lane + 32 * m, q_src + 32 * m);
+                    }
+            }
+            if (lane < COLS && live) dr_copy4(sg + 2 * DP + lane, v_src);        // rg == 0 here
+            if (lane == 31) dr_copy8(sg + 2 * DP + 8, g_src);                   // decay, beta
+            k_src += C; q_src += C; v_src += C; g_src += 2 * dm.H;
+        }
+        ++fetch_t;
+        fetch_stage = fetch_stage + 1 == STAGES ? 0 : fetch_stage + 1;
+        asm volatile("cp.async.commit_group;" ::: "memory");     // one group per token, empty or not
+    };
+    for (int p = 0; p < STAGES - 1; ++p) fetch();
     float* S = state + (size_t)slots[seq] * state_stride + ((size_t)h * D) * dm.V + col;
-    float s[DMAX];
+    float s[ROWS];
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i) s[i] = (live && i < D) ? S[(size_t)i * dm.V] : 0.f;
-    constexpr int PER = DMAX / 32;
-    float kn[PER], qn[PER];
-    {
-        const float* row = qkv + (size_t)first * C;
-#pragma unroll
-        for (int r = 0; r < PER; ++r) {
-            const int i = lane + 32 * r;
-            ks[0][i] = i < D ? row[(dm.G + g) * D + i] : 0.f;
-            qs[0][i] = i < D ? row[g * D + i] : 0.f;
-        }
-    }
-    __syncwarp();
+    for (int j = 0; j < ROWS; ++j) s[j] = (live && row0 + j < D) ? S[(size_t)(row0 + j) * dm.V] : 0.f;
+    float* orow = out + (size_t)first * dm.H * dm.V + h * dm.V + col;
+    int cur_stage = 0;
     for (int t = first; t < last; ++t) {
-        const int cur = (t - first) & 1;
-        if (t + 1 < last) {                                  // the next token's k and q: on their way during the math
-            const float* row = qkv + (size_t)(t + 1) * C;
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");   // this lane's copies of token t
+        __syncwarp();                                                            // ... and the other lanes'
+        fetch();                               // token t + STAGES - 1, into the stage that token t-1 has left
+        const float* sg = ring[cur_stage];
+        cur_stage = cur_stage + 1 == STAGES ? 0 : cur_stage + 1;
+        const float* kc = sg + row0;
+        const float* qc = sg + DP + row0;
+        const float gd = sg[2 * DP + 8], b = sg[2 * DP + 9];
+        const float v = sg[2 * DP + cl];
+        float part[CHUNKS];
 #pragma unroll
-            for (int r = 0; r < PER; ++r) {
-                const int i = lane + 32 * r;
-                kn[r] = i < D ? row[(dm.G + g) * D + i] : 0.f;
-                qn[r] = i < D ? row[g * D + i] : 0.f;
-            }
-        }
-        const float gd = decay[(size_t)t * dm.H + h], b = beta[(size_t)t * dm.H + h];
-        const float v = live ? qkv[(size_t)t * C + 2 * dm.G * D + h * dm.V + col] : 0.f;
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+        for (int c = 0; c < CHUNKS; ++c) {
+            const float4 ka = *reinterpret_cast<const float4*>(kc + 8 * c);
+            const float4 kb = *reinterpret_cast<const float4*>(kc + 8 * c + 4);
+            float* sc = s + 8 * c;
 #pragma unroll
-        for (int i = 0; i < DMAX; i += 4) {
-            const float4 k4 = *reinterpret_cast<const float4*>(&ks[cur][i]);
-            s[i] *= gd; s[i + 1] *= gd; s[i + 2] *= gd; s[i + 3] *= gd;
-            d0 = fmaf(s[i], k4.x, d0); d1 = fmaf(s[i + 1], k4.y, d1);
-            d2 = fmaf(s[i + 2], k4.z, d2); d3 = fmaf(s[i + 3], k4.w, d3);
+            for (int j = 0; j < 8; ++j) sc[j] *= gd;
+            const float d0 = fmaf(sc[4], kb.x, sc[0] * ka.x), d1 = fmaf(sc[5], kb.y, sc[1] * ka.y);
+            const float d2 = fmaf(sc[6], kb.z, sc[2] * ka.z), d3 = fmaf(sc[7], kb.w, sc[3] * ka.w);
+            part[c] = (d0 + d1) + (d2 + d3);
         }
-        const float u = b * (v - ((d0 + d1) + (d2 + d3)));
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DMAX; i += 4) {
-            const float4 k4 = *reinterpret_cast<const float4*>(&ks[cur][i]);
-            const float4 q4 = *reinterpret_cast<const float4*>(&qs[cur][i]);
-            s[i] = fmaf(k4.x, u, s[i]); s[i + 1] = fmaf(k4.y, u, s[i + 1]);
-            s[i + 2] = fmaf(k4.z, u, s[i + 2]); s[i + 3] = fmaf(k4.w, u, s[i + 3]);
-            o0 = fmaf(s[i], q4.x, o0); o1 = fmaf(s[i + 1], q4.y, o1);
-            o2 = fmaf(s[i + 2], q4.z, o2); o3 = fmaf(s[i + 3], q4.w, o3);
-        }
-        if (live) out[(size_t)t * dm.H * dm.V + h * dm.V + col] = (o0 + o1) + (o2 + o3);
-        if (t + 1 < last) {
+        for (int w = 1; w < CHUNKS; w <<= 1)
 #pragma unroll
-            for (int r = 0; r < PER; ++r) {
-                ks[cur ^ 1][lane + 32 * r] = kn[r];
-                qs[cur ^ 1][lane + 32 * r] = qn[r];
-            }
+            for (int c = 0; c < CHUNKS; c += 2 * w) part[c] += part[c + w];
+        float dot = part[0];
+#pragma unroll
+        for (int off = COLS; off < 32; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        const float u = b * (v - dot);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const float4 ka = *reinterpret_cast<const float4*>(kc + 8 * c);
+            const float4 kb = *reinterpret_cast<const float4*>(kc + 8 * c + 4);
+            const float4 qa = *reinterpret_cast<const float4*>(qc + 8 * c);
+            const float4 qb = *reinterpret_cast<const float4*>(qc + 8 * c + 4);
+            float* sc = s + 8 * c;
+            sc[0] = fmaf(ka.x, u, sc[0]); sc[1] = fmaf(ka.y, u, sc[1]); sc[2] = fmaf(ka.z, u, sc[2]); sc[3] = fmaf(ka.w, u, sc[3]);
+            sc[4] = fmaf(kb.x, u, sc[4]); sc[5] = fmaf(kb.y, u, sc[5]); sc[6] = fmaf(kb.z, u, sc[6]); sc[7] = fmaf(kb.w, u, sc[7]);
+            const float o0 = fmaf(sc[4], qb.x, sc[0] * qa.x), o1 = fmaf(sc[5], qb.y, sc[1] * qa.y);
+            const float o2 = fmaf(sc[6], qb.z, sc[2] * qa.z), o3 = fmaf(sc[7], qb.w, sc[3] * qa.w);
+            part[c] = (o0 + o1) + (o2 + o3);
         }
-        __syncwarp();
+#pragma unroll
+        for (int w = 1; w < CHUNKS; w <<= 1)
+#pragma unroll
+            for (int c = 0; c < CHUNKS; c += 2 * w) part[c] += part[c + w];
+        float o = part[0];
+#pragma unroll
+        for (int off = COLS; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+        if (rg == 0 && live) *orow = o;
+        orow += dm.H * dm.V;
+        __syncwarp();                          // every lane has left this stage before a later fetch refills it
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i)
-            if (i < D) S[(size_t)i * dm.V] = s[i];
+        for (int j = 0; j < ROWS; ++j)
+            if (row0 + j < D) S[(size_t)(row0 + j) * dm.V] = s[j];
     }
 }
 
@@ -204,7 +285,7 @@ __global__ void delta_gated_norm_kernel(const float* __restrict__ o, const float
 static int dr_check(const DeltaDims& dm) {
     if (dm.G <= 0 || dm.H <= 0 || dm.D <= 0 || dm.V <= 0 || dm.taps <= 0 || dm.H % dm.G) return NI_ERR_BAD_ARGUMENT;
     if (dm.ld < dm.a_off() + dm.H) return NI_ERR_BAD_ARGUMENT;
-    if (dm.D > 256) return NI_ERR_UNSUPPORTED_SIZE;
+    if (dm.D > 1024) return NI_ERR_UNSUPPORTED_SIZE;      // a warp holds whole columns of a head's state: 32 lanes x 32 rows
     return NI_OK;
 }
 
@@ -212,14 +293,16 @@ static int dr_check(const DeltaDims& dm) {
 NI_EXPORT int ni_delta_prepare(const float* proj, const float* conv_w, const float* a_log, const float* dt_bias,
                                float* state, long long state_stride, const int* seq_of_token, const int* cu_q,
                                const int* slots, int n_tokens, int n_seqs, int G, int H, int D, int V, int taps, int ld,
-                               float* qkv, float* beta, float* decay, cudaStream_t stream) {
+                               float* qkv, float* gates, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     DeltaDims dm{G, H, D, V, taps, ld};
     if (int rc = dr_check(dm)) return rc;
     const int C = dm.C();
-    const int threads = C >= 2048 ? 256 : 128;
-    delta_prepare_kernel<<<n_tokens, threads, 0, stream>>>(proj, conv_w, a_log, dt_bias, state, state_stride,
-                                                           seq_of_token, cu_q, slots, dm, qkv, beta, decay);
+    const int n_units = 2 * G + (H * V + DP_VCHUNK - 1) / DP_VCHUNK;
+    dim3 pgrid(n_tokens, (n_units + DP_WARPS - 1) / DP_WARPS);
+    if (pgrid.y > 65535) return NI_ERR_UNSUPPORTED_SIZE;
+    delta_prepare_kernel<<<pgrid, DP_WARPS * 32, 0, stream>>>(proj, conv_w, a_log, dt_bias, state, state_stride,
+                                                              seq_of_token, cu_q, slots, dm, qkv, gates);
     if (taps > 1) {
         dim3 grid((C + 127) / 128, n_seqs);
         delta_history_kernel<<<grid, 128, 0, stream>>>(proj, state, state_stride, cu_q, slots, dm);
@@ -227,20 +310,26 @@ NI_EXPORT int ni_delta_prepare(const float* proj, const float* conv_w, const flo
     NI_RETURN_LAUNCH_STATUS();
 }
 
-NI_EXPORT int ni_delta_recurrence(const float* qkv, const float* beta, const float* decay, float* state,
-                                  long long state_stride, const int* cu_q, const int* slots, int n_seqs, int G, int H,
-                                  int D, int V, float* out, cudaStream_t stream) {
+NI_EXPORT int ni_delta_recurrence(const float* qkv, const float* gates, float* state,
+                                  long long state_stride, const int* cu_q, const int* slots, int n_tokens, int n_seqs,
+                                  int G, int H, int D, int V, float* out, cudaStream_t stream) {
     if (n_seqs <= 0) return NI_OK;
     DeltaDims dm{G, H, D, V, 1, 2 * G * D + 2 * H * V + 2 * H};
     if (int rc = dr_check(dm)) return rc;
     if (H > 65535 || n_seqs > 65535) return NI_ERR_UNSUPPORTED_SIZE;
-    dim3 grid((V + 31) / 32, H, n_seqs);
-#define LAUNCH(DMAX) \
-    delta_recurrence_kernel<DMAX><<<grid, 32, 0, stream>>>(qkv, beta, decay, state, state_stride, cu_q, slots, dm, out)
-    if (D <= 32) LAUNCH(32);
-    else if (D <= 64) LAUNCH(64);
-    else if (D <= 128) LAUNCH(128);
-    else LAUNCH(256);
+#define LAUNCH(CHUNKS, RG)                                                                                       \
+    do {                                                                                                         \
+        dim3 grid((V + 32 / (RG) - 1) / (32 / (RG)), H, n_seqs);                                                 \
+        delta_recurrence_kernel<CHUNKS, RG><<<grid, 32, 0, stream>>>(qkv, gates, state, state_stride, cu_q,       \
+                                                                     slots, dm, out);                            \
+    } while (0)
+    const bool long_portions = n_tokens >= 8 * n_seqs;       // the same bits either way; see the kernel
+    if (D <= 32) LAUNCH(1, 4);
+    else if (D <= 64) { if (long_portions) LAUNCH(1, 8); else LAUNCH(2, 4); }
+    else if (D <= 128) { if (long_portions) LAUNCH(1, 16); else LAUNCH(4, 4); }
+    else if (D <= 256) { if (long_portions) LAUNCH(1, 32); else LAUNCH(4, 8); }
+    else if (D <= 512) LAUNCH(4, 16);
+    else LAUNCH(4, 32);
 #undef LAUNCH
     NI_RETURN_LAUNCH_STATUS();
 }

@@ -6,6 +6,7 @@
     python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048 --kernel tc
     python -m nanoinfer_b200.kernels.microbench gemm_swap --m 64 --n 2048 --k 2048 --mode add --milestones
     python -m nanoinfer_b200.kernels.microbench decode_fused --batch 8 --context 2048
+    python -m nanoinfer_b200.kernels.microbench delta_rule --batch 8 --tokens 1 --heads 16 --dim 128 --vdim 128
 
 Each case runs its kernel over several distinct copies of its inputs in turn (together
 larger than the L2 cache, so every run reads from HBM), times it with CUDA events after
@@ -179,6 +180,9 @@ def attention_decode(args) -> None:
     n_pages = b * pages_per_seq
     caches = [(torch.randn(n_pages, hkv, page, hd, device=DEV, generator=g).to(torch.bfloat16),
                torch.randn(n_pages, hkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)) for _ in range(copies)]
+    if getattr(args, "shared_kv", False):          # keys and values are the same pages (attention over a latent cache)
+        caches = [(kc, kc) for kc, _ in caches]
+        kv_bytes //= 2
     table = torch.randperm(n_pages, device=DEV, generator=g).int().view(b, pages_per_seq)
     q = torch.randn(b, hq * hd, device=DEV, generator=g).to(torch.bfloat16)
     out = torch.empty_like(q)
@@ -347,6 +351,41 @@ def decode_fused(args) -> None:
           f"chain of kernels {results[False]:.3f} ms, fused kernel {results[True]:.3f} ms")
 
 
+def delta_rule(args) -> None:
+    """The gated delta rule's kernels at --batch requests of --tokens tokens each: the preparation (convolution,
+    unit norms, gates), the recurrence, the gated norm.  States of several request sets are used in turn, so that
+    single-token steps read theirs from HBM."""
+    b, t, G, H, D, V, taps = args.batch, args.tokens, args.kv_heads, args.heads, args.dim, args.vdim, args.taps
+    n = b * t
+    C, N = 2 * G * D + H * V, 2 * G * D + 2 * H * V + 2 * H
+    size = H * D * V + (taps - 1) * C
+    copies = max(2, min(32, -(-2 * L2_BYTES // (b * size * 4)))) if t == 1 else 2
+    g = torch.Generator(device=DEV).manual_seed(0)
+    states = [torch.randn(b, size, device=DEV, generator=g) * 0.1 for _ in range(copies)]
+    proj = torch.randn(n, N, device=DEV, generator=g)
+    conv_w = torch.randn(C, taps, device=DEV, generator=g) * 0.5
+    a_log, dt_bias = torch.zeros(H, device=DEV), torch.zeros(H, device=DEV)
+    norm_w = torch.ones(V, device=DEV)
+    cu = torch.arange(0, n + 1, t, dtype=torch.int32, device=DEV)
+    seq = torch.repeat_interleave(torch.arange(b, device=DEV), t).int()
+    slots = torch.arange(b, dtype=torch.int32, device=DEV)
+    qkv = torch.empty(n, C, device=DEV)
+    gates = torch.empty(n, H, 2, device=DEV)
+    o = torch.empty(n, H * V, device=DEV)
+    y = torch.empty(n, H * V, dtype=torch.bfloat16, device=DEV)
+    us_prep = _time([lambda st=st: ops.delta_prepare(proj, conv_w, a_log, dt_bias, st, seq, cu, slots, b, G, H, D, V, taps,
+                                                     qkv, gates) for st in states], args.iters)
+    us_rec = _time([lambda st=st: ops.delta_recurrence(qkv, gates, st, cu, slots, b, G, H, D, V, o) for st in states],
+                   args.iters)
+    us_norm = _time([lambda: ops.delta_gated_norm(o, proj, norm_w, 1e-6, G, H, D, V, y)], args.iters)
+    state_bytes = 2 * b * H * D * V * 4                      # S read and written once per step
+    flops = 8.0 * n * H * D * V                              # two passes of multiply-add over S per token, decay included
+    print(f"delta_rule batch={b} tokens={t} heads={H}/{G} dim={D} vdim={V} taps={taps}: prepare {us_prep:.2f} us "
+          f"({n * (N + C + 2 * H) * 4 / us_prep / 1e3:.0f} GB/s), recurrence {us_rec:.2f} us "
+          f"({state_bytes / us_rec / 1e3:.0f} GB/s of state, {flops / us_rec / 1e6:.2f} TFLOP/s FP32), "
+          f"gated norm {us_norm:.2f} us ({n * H * V * (4 + 4 + 2) / us_norm / 1e3:.0f} GB/s)")
+
+
 def main() -> None:
     ops.require_cuda()
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -404,6 +443,15 @@ def main() -> None:
     p.add_argument("--shape", default="llama-3.2-1b")
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has")
     p.set_defaults(fn=decode_fused)
+    p = sub.add_parser("delta_rule")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--tokens", type=int, default=1)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--dim", type=int, default=128)
+    p.add_argument("--vdim", type=int, default=128)
+    p.add_argument("--taps", type=int, default=4)
+    p.set_defaults(fn=delta_rule)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
@@ -418,6 +466,7 @@ def main() -> None:
         p.add_argument("--copies", type=int, default=0, help="decode: cache copies used in turn (default: enough to exceed L2; 1: the cache stays in L2)")
         p.add_argument("--balanced", action="store_true", help="decode: the kernel that deals the keys evenly over a fixed grid")
         p.add_argument("--ragged", action="store_true", help="decode: contexts from a quarter of --context up to it")
+        p.add_argument("--shared-kv", action="store_true", help="decode: keys and values are the same pages (a latent cache)")
         p.add_argument("--scratch-merge", action="store_true",
                        help="decode: merge the splits through global scratch and tickets, not inside a cluster")
         p.set_defaults(fn=fn)

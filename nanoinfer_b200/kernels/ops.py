@@ -48,8 +48,8 @@ _SIGNATURES = {
         "ni_gelu_table_gate": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     },
     "delta_rule": {
-        "ni_delta_prepare": [_P, _P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
-        "ni_delta_recurrence": [_P, _P, _P, _P, _LL, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "ni_delta_prepare": [_P, _P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
+        "ni_delta_recurrence": [_P, _P, _P, _LL, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "ni_delta_gated_norm": [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _I, _P],
     },
     "latent": {
@@ -314,7 +314,7 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       block_table: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, window: Optional[int], scale: float,
                       token_list: Optional[torch.Tensor] = None, head_slopes: Optional[torch.Tensor] = None) -> None:
-    """The plain attention kernel (any dtype, any head size up to 256).  ``token_list``
+    """The plain attention kernel (any dtype, any head size up to 512).  ``token_list``
     int32 [n] restricts it to those tokens of the step.  ``head_slopes`` float32 [Hq] adds
     slope[h] * (key position - query position) to the scaled scores of head h."""
     if head_slopes is not None and head_slopes.numel() != n_q_heads:
@@ -324,8 +324,8 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError("attention: q and out must be [T, Hq * head_dim]")
     if not (q.dtype == out.dtype == k_pages.dtype == v_pages.dtype):
         raise KernelError("attention: all operands must share one dtype")
-    if head_dim > 256:
-        raise KernelError(f"attention: head_dim {head_dim} > 256 is not supported")
+    if head_dim > 512:
+        raise KernelError(f"attention: head_dim {head_dim} > 512 is not supported")
     _check(load("attention_generic").ni_attention_generic(
         _dev(q, "q"), _code(q, "q"), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
         _dev(out, "out"), _dev(token_list, "token_list", torch.int32) if token_list is not None else None,
@@ -410,13 +410,13 @@ def gelu_table_gate(gate: torch.Tensor, tokens: torch.Tensor, table: torch.Tenso
 
 
 def delta_prepare(proj, conv_w, a_log, dt_bias, state, seq_of_token, cu_q, slots, n_seqs, n_q_heads_kv, n_heads, dim,
-                  vdim, taps, qkv, beta, decay) -> None:
+                  vdim, taps, qkv, gates) -> None:
     """The gated delta rule's per-token inputs from the fused projection ``proj`` (float32 [T, ld], columns
-    q | k | v | gate | b | a): convolution + silu, unit q and k, beta, decay; then each request's new
-    convolution history in ``state`` (float32 [slots, H D V + (taps - 1) C])."""
+    q | k | v | gate | b | a): convolution + silu, unit q and k -> qkv [T, C]; decay and beta -> gates [T, H, 2];
+    then each request's new convolution history in ``state`` (float32 [slots, H D V + (taps - 1) C])."""
     n = proj.shape[0]
     c = 2 * n_q_heads_kv * dim + n_heads * vdim
-    if qkv.shape != (n, c) or beta.shape != (n, n_heads) or decay.shape != (n, n_heads) or conv_w.shape != (c, taps):
+    if qkv.shape != (n, c) or gates.shape != (n, n_heads, 2) or conv_w.shape != (c, taps):
         raise KernelError("delta_prepare: shapes do not agree")
     if state.shape[1] != n_heads * dim * vdim + (taps - 1) * c:
         raise KernelError("delta_prepare: the state has another size")
@@ -425,20 +425,20 @@ def delta_prepare(proj, conv_w, a_log, dt_bias, state, seq_of_token, cu_q, slots
         _dev(proj, "proj", f32), _dev(conv_w, "conv_w", f32), _dev(a_log, "a_log", f32), _dev(dt_bias, "dt_bias", f32),
         _dev(state, "state", f32), state.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
         _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), n, n_seqs, n_q_heads_kv, n_heads, dim, vdim,
-        taps, proj.shape[1], _dev(qkv, "qkv", f32), _dev(beta, "beta", f32), _dev(decay, "decay", f32), _stream()),
+        taps, proj.shape[1], _dev(qkv, "qkv", f32), _dev(gates, "gates", f32), _stream()),
         "delta_prepare")
 
 
-def delta_recurrence(qkv, beta, decay, state, cu_q, slots, n_seqs, n_q_heads_kv, n_heads, dim, vdim, out) -> None:
+def delta_recurrence(qkv, gates, state, cu_q, slots, n_seqs, n_q_heads_kv, n_heads, dim, vdim, out) -> None:
     """S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q for every token of every request, in order;
     S float32 [H, D, V] at the start of each row of ``state``; out float32 [T, H V]."""
     f32 = torch.float32
     if out.shape != (qkv.shape[0], n_heads * vdim):
         raise KernelError("delta_recurrence: out must be [T, H V]")
     _check(load("delta_rule").ni_delta_recurrence(
-        _dev(qkv, "qkv", f32), _dev(beta, "beta", f32), _dev(decay, "decay", f32), _dev(state, "state", f32),
-        state.shape[1], _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), n_seqs, n_q_heads_kv,
-        n_heads, dim, vdim, _dev(out, "out", f32), _stream()), "delta_recurrence")
+        _dev(qkv, "qkv", f32), _dev(gates, "gates", f32), _dev(state, "state", f32),
+        state.shape[1], _dev(cu_q, "cu_q", torch.int32), _dev(slots, "slots", torch.int32), qkv.shape[0], n_seqs,
+        n_q_heads_kv, n_heads, dim, vdim, _dev(out, "out", f32), _stream()), "delta_recurrence")
 
 
 def delta_gated_norm(o, proj, weight, eps, n_q_heads_kv, n_heads, dim, vdim, y) -> None:

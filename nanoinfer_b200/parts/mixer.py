@@ -248,8 +248,8 @@ class LatentAttention(PagedAttendMixin, Part):
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         Part.__init__(self, spec, hidden_size, weights, rt)
         h, d, v, r, own = self._dims(spec)
-        if h <= 0 or d <= 0 or v <= 0 or not 0 < r <= 256:
-            raise ConfigError(f"latent attention: heads, sizes must be positive and the latent rank at most 256 (got {r})")
+        if h <= 0 or d <= 0 or v <= 0 or not 0 < r <= 512:
+            raise ConfigError(f"latent attention: heads and sizes must be positive and the latent rank at most 512 (got {r})")
         # what the attention kernels see: h query heads over one shared head of size r
         self.n_heads, self.n_kv, self.head_dim = h, 1, r
         self.qk_dim, self.value_dim, self.rank, self.own_latent = d, v, r, own

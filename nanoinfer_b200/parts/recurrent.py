@@ -54,8 +54,8 @@ class GatedDeltaRule(Part):
         g, h, d, v, taps = self._dims(spec)
         if g <= 0 or h <= 0 or h % g:
             raise ConfigError("gated delta rule: heads must be a positive multiple of kv_heads")
-        if not 0 < d <= 256:
-            raise ConfigError(f"gated delta rule: a key size of {d} is not supported (1 to 256)")
+        if not 0 < d <= 1024:
+            raise ConfigError(f"gated delta rule: a key size of {d} is not supported (1 to 1024)")
         if v <= 0 or taps <= 0:
             raise ConfigError("gated delta rule: value size and convolution taps must be positive")
         self.G, self.H, self.D, self.V, self.taps = g, h, d, v, taps
@@ -80,11 +80,11 @@ class GatedDeltaRule(Part):
         g, h, d, v = self.G, self.H, self.D, self.V
         proj = rt.linear(x, self.w_in, out_dtype=f32)
         qkv = rt.empty(n, self.channels, dtype=f32)
-        beta, decay = rt.empty(n, h, dtype=f32), rt.empty(n, h, dtype=f32)
+        gates = rt.empty(n, h, 2, dtype=f32)
         ops.delta_prepare(proj, self.conv_w, self.a_log, self.dt_bias, cache.state, ctx.seq_of_token, ctx.cu_q,
-                          ctx.slots, ctx.n_seqs, g, h, d, v, self.taps, qkv, beta, decay)
+                          ctx.slots, ctx.n_seqs, g, h, d, v, self.taps, qkv, gates)
         o = rt.empty(n, h * v, dtype=f32)
-        ops.delta_recurrence(qkv, beta, decay, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, g, h, d, v, o)
+        ops.delta_recurrence(qkv, gates, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, g, h, d, v, o)
         y = rt.empty(n, h * v)
         ops.delta_gated_norm(o, proj, self.norm_w, self.eps, g, h, d, v, y)
         return rt.linear(y, self.w_o, residual=residual)

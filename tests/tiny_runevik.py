@@ -35,8 +35,9 @@ R3 = {"architecture": "Runevik", "vocab": 200, "width": 64, "norm": {"eps": 1e-6
                  latent(1, 24, 40, 128, 0.15, 0, kv_from=1)]}
 
 # Standard deviations that make every mechanism matter in a random model: activation numbers of order one,
-# peaked attention (scores of order one), output projections that weigh as much as the stream.
-LIVELY = {"act": 0.6, "uk": 0.25, "q": 0.12, "dkv": 0.12, "uv": 0.15, "o": 0.08, "v": 0.1, "k": 0.1, "g": 0.1,
+# peaked attention (scores with a standard deviation of 1 to 2; sharper ones would pass bfloat16 rounding
+# through the exponential at full size), output projections that weigh as much as the stream.
+LIVELY = {"act": 0.6, "uk": 0.25, "q": 0.05, "dkv": 0.12, "uv": 0.15, "o": 0.08, "v": 0.1, "k": 0.1, "g": 0.1,
           "up": 0.1, "down": 0.08, "gate": 0.1, "proj": 0.2, "layer_inputs": 0.5, "weight": 0.5, "b": 0.1, "a": 0.1,
           "q.conv": 0.5, "k.conv": 0.5, "v.conv": 0.5, "dt_bias": 0.5, "A_log": 0.5}
 
