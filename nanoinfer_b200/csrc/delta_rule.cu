@@ -201,6 +201,7 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
     for (int j = 0; j < ROWS; ++j) s[j] = (live && row0 + j < D) ? S[(size_t)(row0 + j) * dm.V] : 0.f;
     float* orow = out + (size_t)first * dm.H * dm.V + h * dm.V + col;
     int cur_stage = 0;
+    float o_pending = 0.f;
     for (int t = first; t < last; ++t) {
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");   // this lane's copies of token t
         __syncwarp();                                                            // ... and the other lanes'
@@ -228,8 +229,15 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
 #pragma unroll
             for (int c = 0; c < CHUNKS; c += 2 * w) part[c] += part[c + w];
         float dot = part[0];
+        // the lanes' partial sums of this token's S^T k and of the token before's S^T q travel together: two
+        // independent shuffles per level instead of two trees one after the other
 #pragma unroll
-        for (int off = COLS; off < 32; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        for (int off = COLS; off < 32; off <<= 1) {
+            dot += __shfl_xor_sync(0xffffffffu, dot, off);
+            o_pending += __shfl_xor_sync(0xffffffffu, o_pending, off);
+        }
+        if (t > first && rg == 0 && live) orow[0] = o_pending;
+        if (t > first) orow += dm.H * dm.V;
         const float u = b * (v - dot);
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
@@ -248,13 +256,12 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
         for (int w = 1; w < CHUNKS; w <<= 1)
 #pragma unroll
             for (int c = 0; c < CHUNKS; c += 2 * w) part[c] += part[c + w];
-        float o = part[0];
-#pragma unroll
-        for (int off = COLS; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-        if (rg == 0 && live) *orow = o;
-        orow += dm.H * dm.V;
+        o_pending = part[0];                   // summed over the lanes while the next token's S^T k is
         __syncwarp();                          // every lane has left this stage before a later fetch refills it
     }
+#pragma unroll
+    for (int off = COLS; off < 32; off <<= 1) o_pending += __shfl_xor_sync(0xffffffffu, o_pending, off);
+    if (rg == 0 && live) orow[0] = o_pending;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (live) {
 #pragma unroll

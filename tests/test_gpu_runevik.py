@@ -56,14 +56,16 @@ def _sensitivity(cfg, w, reqs, want):
     size of a bfloat16 rounding: {(request, position): factor >= 1}.  Where the delta rule subtracts a good
     prediction, or a norm divides by a small mean, a position can be ten times as sensitive as most."""
     g = torch.Generator().manual_seed(0)
-    shaken = {k: v.double() * (1 + 2.0 ** -8 * (torch.rand(v.shape, generator=g, dtype=torch.float64) - 0.5)) for k, v in w.items()}
-    plain = PlainRunevik(cfg, shaken)
     moved = {}
-    for rid, toks in reqs.items():
-        out = plain.run(toks, plain.new_state())[0].float()
-        rel = (out - want[rid]).pow(2).mean(1).sqrt() / want[rid].pow(2).mean(1).sqrt()
-        for pos in range(len(toks)):
-            moved[(rid, pos)] = rel[pos].item()
+    for trial in range(3):                       # a position's sensitivity depends on the direction: the largest of three
+        shaken = {k: v.double() * (1 + 2.0 ** -8 * (torch.rand(v.shape, generator=g, dtype=torch.float64) - 0.5))
+                  for k, v in w.items()}
+        plain = PlainRunevik(cfg, shaken)
+        for rid, toks in reqs.items():
+            out = plain.run(toks, plain.new_state())[0].float()
+            rel = (out - want[rid]).pow(2).mean(1).sqrt() / want[rid].pow(2).mean(1).sqrt()
+            for pos in range(len(toks)):
+                moved[(rid, pos)] = max(moved.get((rid, pos), 0.0), rel[pos].item())
     median = sorted(moved.values())[len(moved) // 2]
     return {k: max(1.0, v / (3.0 * median)) for k, v in moved.items()}
 
