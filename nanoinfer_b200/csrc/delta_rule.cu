@@ -119,8 +119,9 @@ __global__ void delta_history_kernel(const float* __restrict__ proj, float* __re
 // lane followed by log2(RG) shuffles.  The order of every sum is fixed by the chunk numbers alone (8 rows in
 // four interleaved chains, then a binary tree over the chunk index from its lowest bit up), so the two
 // layouts launched below - few lanes per column for single tokens, whose cost is reading and writing S in
-// whole 32-byte sectors, and many lanes per column for long portions, whose cost is the chain of dependent
-// operations per token - give the same bits.  Lanes of one row group sit side by side and read neighbouring
+// whole 32-byte sectors, and more lanes per column for long portions, whose cost is the chain of dependent
+// operations per token - give the same bits.  (Key size 128, 16 heads, measured: one request of 2,048 tokens
+// 695 us with 4 lanes per column, 613 us with 8, 647 us with 16; a batch of 8 single tokens 8.7 / 11.2 / 27.8 us.)  Lanes of one row group sit side by side and read neighbouring
 // columns.  No block barrier.  What a token brings (k, q, the warp's values, decay, beta) travels through a
 // ring of tokens in shared memory, filled by asynchronous copies that run ahead of the arithmetic.
 #define DR_MAX_STAGES 8
@@ -156,10 +157,14 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
     const int first = cu_q[seq], last = cu_q[seq + 1];
     if (first >= last) return;
     const bool wide = (D % 4 == 0) && (C % 4 == 0);        // rows of k and q start on 16-byte boundaries
-    for (int st = 0; st < STAGES; ++st) {                  // entries that no copy ever writes
-        for (int i = lane; i < DP; i += 32)
-            if (i >= D) ring[st][i] = ring[st][DP + i] = 0.f;
-        if (lane < COLS && !live) ring[st][2 * DP + lane] = 0.f;
+    const bool padded = D != DP;                           // same for the whole launch
+    const bool ragged = blockIdx.x * COLS + COLS > dm.V;   // same for the whole warp: some of its columns do not exist
+    if (padded || ragged) {                                // entries that no copy ever writes
+        for (int st = 0; st < STAGES; ++st) {
+            for (int i = lane; i < DP; i += 32)
+                if (i >= D) ring[st][i] = ring[st][DP + i] = 0.f;
+            if (lane < COLS && !live) ring[st][2 * DP + lane] = 0.f;
+        }
     }
     // Each lane's sources of the next token to fetch, advanced by a row per token; its place in the ring likewise.
     const float* row = qkv + (size_t)first * C;
@@ -195,10 +200,16 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
         asm volatile("cp.async.commit_group;" ::: "memory");     // one group per token, empty or not
     };
     for (int p = 0; p < STAGES - 1; ++p) fetch();
-    float* S = state + (size_t)slots[seq] * state_stride + ((size_t)h * D) * dm.V + col;
+    float* S = state + (size_t)slots[seq] * state_stride + ((size_t)h * D + row0) * dm.V + col;   // this lane's first row
     float s[ROWS];
+    if (!padded && !ragged) {
+        const float* sp = S;
 #pragma unroll
-    for (int j = 0; j < ROWS; ++j) s[j] = (live && row0 + j < D) ? S[(size_t)(row0 + j) * dm.V] : 0.f;
+        for (int j = 0; j < ROWS; ++j, sp += dm.V) s[j] = *sp;
+    } else {
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) s[j] = (live && row0 + j < D) ? S[(size_t)j * dm.V] : 0.f;
+    }
     float* orow = out + (size_t)first * dm.H * dm.V + h * dm.V + col;
     int cur_stage = 0;
     float o_pending = 0.f;
@@ -263,10 +274,14 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
     for (int off = COLS; off < 32; off <<= 1) o_pending += __shfl_xor_sync(0xffffffffu, o_pending, off);
     if (rg == 0 && live) orow[0] = o_pending;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (live) {
+    if (!padded && !ragged) {
+        float* sp = S;
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j, sp += dm.V) *sp = s[j];
+    } else if (live) {
 #pragma unroll
         for (int j = 0; j < ROWS; ++j)
-            if (row0 + j < D) S[(size_t)(row0 + j) * dm.V] = s[j];
+            if (row0 + j < D) S[(size_t)j * dm.V] = s[j];
     }
 }
 
@@ -330,13 +345,32 @@ NI_EXPORT int ni_delta_recurrence(const float* qkv, const float* gates, float* s
         delta_recurrence_kernel<CHUNKS, RG><<<grid, 32, 0, stream>>>(qkv, gates, state, state_stride, cu_q,       \
                                                                      slots, dm, out);                            \
     } while (0)
-    const bool long_portions = n_tokens >= 8 * n_seqs;       // the same bits either way; see the kernel
-    if (D <= 32) LAUNCH(1, 4);
-    else if (D <= 64) { if (long_portions) LAUNCH(1, 8); else LAUNCH(2, 4); }
-    else if (D <= 128) { if (long_portions) LAUNCH(1, 16); else LAUNCH(4, 4); }
-    else if (D <= 256) { if (long_portions) LAUNCH(1, 32); else LAUNCH(4, 8); }
-    else if (D <= 512) LAUNCH(4, 16);
-    else LAUNCH(4, 32);
+    // Lanes per column (RG): single tokens take the fewest (whole sectors of S); long portions take the fewest that
+    // still give every scheduler a warp or so (3 warps per SM and more: measured at key size 128, one request of
+    // 2,048 tokens, 16 heads: 695 / 613 / 647 us with 4 / 8 / 16 lanes; 8 heads: 16 lanes ahead of 8; 8 requests
+    // of 512 tokens: 483 / 488 / 734 us).  The bits are the same whichever is taken.
+    const bool long_portions = n_tokens >= 8 * n_seqs;
+    const int chunks_total = D <= 32 ? 4 : D <= 64 ? 8 : D <= 128 ? 16 : D <= 256 ? 32 : D <= 512 ? 64 : 128;
+    int rg = chunks_total / 4 < 4 ? 4 : chunks_total / 4;             // 4 chunks per lane (1 where D <= 32)
+    if (long_portions)
+        while (rg < 32 && rg < chunks_total &&
+               (long long)n_seqs * H * ((V + 32 / rg - 1) / (32 / rg)) < 3LL * ni_sm_count())
+            rg *= 2;
+    switch (chunks_total * 100 + rg) {
+        case 404: LAUNCH(1, 4); break;
+        case 804: LAUNCH(2, 4); break;
+        case 808: LAUNCH(1, 8); break;
+        case 1604: LAUNCH(4, 4); break;
+        case 1608: LAUNCH(2, 8); break;
+        case 1616: LAUNCH(1, 16); break;
+        case 3208: LAUNCH(4, 8); break;
+        case 3216: LAUNCH(2, 16); break;
+        case 3232: LAUNCH(1, 32); break;
+        case 6416: LAUNCH(4, 16); break;
+        case 6432: LAUNCH(2, 32); break;
+        case 12832: LAUNCH(4, 32); break;
+        default: return NI_ERR_UNSUPPORTED_SIZE;
+    }
 #undef LAUNCH
     NI_RETURN_LAUNCH_STATUS();
 }

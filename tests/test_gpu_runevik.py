@@ -302,12 +302,14 @@ def test_token_input_and_polynorm_alone(tmp_path, dtype):
         ru.compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, label="token input")
 
 
+@pytest.mark.parametrize("heads, rank", [(17, 288), (20, 64), (3, 96), (18, 128)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_wide_latent_and_many_heads(tmp_path, dtype):
-    """A latent wider than any head of the fast attention kernels (288) under 17 query heads, and a second layer
-    that borrows it with other sizes: the plain attention kernel takes both."""
+def test_latent_ranks_and_head_counts(tmp_path, dtype, heads, rank):
+    """Latents and head counts that the fast attention kernels take only in part or not at all - a latent wider
+    than any of their heads (288), more than 16 heads over the shared row (the split-K kernel's limit), a rank of
+    96 (prompt kernel only) - and a second layer that borrows the latent with other sizes."""
     raw = {"architecture": "Runevik", "vocab": 90, "width": 80, "norm": {"eps": 1e-6},
-           "layers": [tr.latent(17, 8, 8, 288, 0.35, 0), tr.latent(2, 24, 40, 288, 0.2, 48, kv_from=0)]}
+           "layers": [tr.latent(heads, 8, 8, rank, 0.35, 0), tr.latent(2, 24, 40, rank, 0.2, 48, kv_from=0)]}
     d = str(tmp_path / "m")
     tr.write_model(d, raw, 21)
     cfg, w = load_plain(d)
@@ -315,7 +317,7 @@ def test_wide_latent_and_many_heads(tmp_path, dtype):
     reqs = {"a": random_tokens(90, 45, 1), "b": random_tokens(90, 18, 2)}
     want = {rid: plain.run(toks, plain.new_state())[0].float() for rid, toks in reqs.items()}
     steps = ru.mixed(reqs, max_live=2)
-    _compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, label="wide latent")
+    _compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, label=f"latent {heads} x {rank}")
 
 
 # ---- whole models, cut in four ways ---------------------------------------------------------------------
