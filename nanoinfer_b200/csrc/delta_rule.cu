@@ -11,9 +11,10 @@
 // (G heads of q/k, H heads of v; head h reads q/k head h / (H / G)).  A request's state is a flat
 // FP32 vector [ S: H D V | history: (taps-1) C ] with C = 2 G D + H V, found through slots[].
 //
-// Four kernels, all FP32 inside:
+// Three launches, all FP32 inside:
 //   delta_prepare      per token: convolution + silu, unit norms, beta, decay
-//   delta_history      per request: the new last taps-1 inputs (after delta_prepare has read the old)
+//   (delta_history     per request: the new last taps-1 inputs; extra blocks of the gated norm's launch, which
+//                      comes after delta_prepare has read the old ones)
 //   delta_recurrence   per (request, head, a few value columns): its tokens one after the other
 //   delta_gated_norm   per token and head: o / rms(o) * weight * silu(gate)
 // Prompt portions and single tokens are the same case; a token's result depends only on its own
@@ -100,10 +101,9 @@ delta_prepare_kernel(const float* __restrict__ proj, const float* __restrict__ c
 
 // The request's new history: its last taps-1 inputs.  One thread per channel walks j upwards, so a
 // portion shorter than the history shifts the old entries in place (it reads index j + q_len > j).
-__global__ void delta_history_kernel(const float* __restrict__ proj, float* __restrict__ state, long long state_stride,
-                                     const int* __restrict__ cu_q, const int* __restrict__ slots, DeltaDims dm) {
-    const int seq = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+__device__ __forceinline__ void delta_history(const float* __restrict__ proj, float* __restrict__ state,
+                                              long long state_stride, const int* __restrict__ cu_q,
+                                              const int* __restrict__ slots, const DeltaDims& dm, int seq, int c) {
     const int C = dm.C();
     if (c >= C) return;
     const int first = cu_q[seq], q_len = cu_q[seq + 1] - first;
@@ -286,10 +286,20 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
 }
 
 // y[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]); one warp per (t, h).
+// The blocks behind those (from norm_blocks on) write the requests' new convolution history: by now the
+// preparation, which read the old one, has ended, and one launch less stands between two steps' products.
 template <typename T>
 __global__ void delta_gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ proj,
                                         const float* __restrict__ weight, float eps, DeltaDims dm, int n_tokens,
-                                        T* __restrict__ y) {
+                                        T* __restrict__ y, int norm_blocks, int hist_blocks_per_seq,
+                                        float* __restrict__ state, long long state_stride,
+                                        const int* __restrict__ cu_q, const int* __restrict__ slots) {
+    if ((int)blockIdx.x >= norm_blocks) {
+        const int hb = blockIdx.x - norm_blocks;
+        delta_history(proj, state, state_stride, cu_q, slots, dm, hb / hist_blocks_per_seq,
+                      (hb % hist_blocks_per_seq) * blockDim.x + threadIdx.x);
+        return;
+    }
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * dm.H) return;
     const int lane = threadIdx.x & 31;
@@ -311,7 +321,8 @@ static int dr_check(const DeltaDims& dm) {
     return NI_OK;
 }
 
-// Convolution, activations, unit norms, beta and decay of the step's tokens, then the new history.
+// Convolution, activations, unit norms, beta and decay of the step's tokens (the new history is written by
+// ni_delta_gated_norm, which every step runs after this).
 NI_EXPORT int ni_delta_prepare(const float* proj, const float* conv_w, const float* a_log, const float* dt_bias,
                                float* state, long long state_stride, const int* seq_of_token, const int* cu_q,
                                const int* slots, int n_tokens, int n_seqs, int G, int H, int D, int V, int taps, int ld,
@@ -325,10 +336,6 @@ NI_EXPORT int ni_delta_prepare(const float* proj, const float* conv_w, const flo
     if (pgrid.y > 65535) return NI_ERR_UNSUPPORTED_SIZE;
     delta_prepare_kernel<<<pgrid, DP_WARPS * 32, 0, stream>>>(proj, conv_w, a_log, dt_bias, state, state_stride,
                                                               seq_of_token, cu_q, slots, dm, qkv, gates);
-    if (taps > 1) {
-        dim3 grid((C + 127) / 128, n_seqs);
-        delta_history_kernel<<<grid, 128, 0, stream>>>(proj, state, state_stride, cu_q, slots, dm);
-    }
     NI_RETURN_LAUNCH_STATUS();
 }
 
@@ -375,19 +382,25 @@ NI_EXPORT int ni_delta_recurrence(const float* qkv, const float* gates, float* s
     NI_RETURN_LAUNCH_STATUS();
 }
 
+// The gated norm of the step's read-outs, and the requests' new convolution history (taps > 1).
 NI_EXPORT int ni_delta_gated_norm(const float* o, const float* proj, const float* weight, float eps, int n_tokens,
-                                  int G, int H, int D, int V, int ld, void* y, int y_dtype, cudaStream_t stream) {
+                                  int n_seqs, int G, int H, int D, int V, int taps, int ld, void* y, int y_dtype,
+                                  float* state, long long state_stride, const int* cu_q, const int* slots,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
-    DeltaDims dm{G, H, D, V, 1, ld};
+    DeltaDims dm{G, H, D, V, taps, ld};
     if (int rc = dr_check(dm)) return rc;
     const int warps = 4;
-    const long long blocks = ((long long)n_tokens * H + warps - 1) / warps;
+    const long long norm_blocks = ((long long)n_tokens * H + warps - 1) / warps;
+    const int per_seq = taps > 1 ? (dm.C() + warps * 32 - 1) / (warps * 32) : 0;
+    const long long blocks = norm_blocks + (long long)per_seq * n_seqs;
     if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
     if (y_dtype == NI_DTYPE_F32)
-        delta_gated_norm_kernel<float><<<(int)blocks, warps * 32, 0, stream>>>(o, proj, weight, eps, dm, n_tokens, (float*)y);
+        delta_gated_norm_kernel<float><<<(int)blocks, warps * 32, 0, stream>>>(
+            o, proj, weight, eps, dm, n_tokens, (float*)y, (int)norm_blocks, per_seq, state, state_stride, cu_q, slots);
     else if (y_dtype == NI_DTYPE_BF16)
-        delta_gated_norm_kernel<__nv_bfloat16><<<(int)blocks, warps * 32, 0, stream>>>(o, proj, weight, eps, dm, n_tokens,
-                                                                                       (__nv_bfloat16*)y);
+        delta_gated_norm_kernel<__nv_bfloat16><<<(int)blocks, warps * 32, 0, stream>>>(
+            o, proj, weight, eps, dm, n_tokens, (__nv_bfloat16*)y, (int)norm_blocks, per_seq, state, state_stride, cu_q, slots);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();

@@ -377,7 +377,7 @@ def delta_rule(args) -> None:
                                                      qkv, gates) for st in states], args.iters)
     us_rec = _time([lambda st=st: ops.delta_recurrence(qkv, gates, st, cu, slots, b, G, H, D, V, o) for st in states],
                    args.iters)
-    us_norm = _time([lambda: ops.delta_gated_norm(o, proj, norm_w, 1e-6, G, H, D, V, y)], args.iters)
+    us_norm = _time([lambda: ops.delta_gated_norm(o, proj, norm_w, 1e-6, G, H, D, V, y, states[0], cu, slots, b, taps)], args.iters)
     state_bytes = 2 * b * H * D * V * 4                      # S read and written once per step
     flops = 8.0 * n * H * D * V                              # two passes of multiply-add over S per token, decay included
     print(f"delta_rule batch={b} tokens={t} heads={H}/{G} dim={D} vdim={V} taps={taps}: prepare {us_prep:.2f} us "

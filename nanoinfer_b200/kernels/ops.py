@@ -50,7 +50,7 @@ _SIGNATURES = {
     "delta_rule": {
         "ni_delta_prepare": [_P, _P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
         "ni_delta_recurrence": [_P, _P, _P, _LL, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
-        "ni_delta_gated_norm": [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+        "ni_delta_gated_norm": [_P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _LL, _P, _P, _P],
     },
     "latent": {
         "ni_latent_norm_write": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -412,8 +412,9 @@ def gelu_table_gate(gate: torch.Tensor, tokens: torch.Tensor, table: torch.Tenso
 def delta_prepare(proj, conv_w, a_log, dt_bias, state, seq_of_token, cu_q, slots, n_seqs, n_q_heads_kv, n_heads, dim,
                   vdim, taps, qkv, gates) -> None:
     """The gated delta rule's per-token inputs from the fused projection ``proj`` (float32 [T, ld], columns
-    q | k | v | gate | b | a): convolution + silu, unit q and k -> qkv [T, C]; decay and beta -> gates [T, H, 2];
-    then each request's new convolution history in ``state`` (float32 [slots, H D V + (taps - 1) C])."""
+    q | k | v | gate | b | a): convolution + silu, unit q and k -> qkv [T, C]; decay and beta -> gates [T, H, 2].
+    It reads each request's convolution history in ``state`` (float32 [slots, H D V + (taps - 1) C]); the new
+    history is written by delta_gated_norm, which must follow in the same step."""
     n = proj.shape[0]
     c = 2 * n_q_heads_kv * dim + n_heads * vdim
     if qkv.shape != (n, c) or gates.shape != (n, n_heads, 2) or conv_w.shape != (c, taps):
@@ -441,14 +442,17 @@ def delta_recurrence(qkv, gates, state, cu_q, slots, n_seqs, n_q_heads_kv, n_hea
         n_q_heads_kv, n_heads, dim, vdim, _dev(out, "out", f32), _stream()), "delta_recurrence")
 
 
-def delta_gated_norm(o, proj, weight, eps, n_q_heads_kv, n_heads, dim, vdim, y) -> None:
-    """y[t, h, :] = o[t, h, :] / rms * weight * silu(gate[t, h, :]), gate = its columns of ``proj``."""
+def delta_gated_norm(o, proj, weight, eps, n_q_heads_kv, n_heads, dim, vdim, y, state, cu_q, slots, n_seqs, taps) -> None:
+    """y[t, h, :] = o[t, h, :] / rms * weight * silu(gate[t, h, :]), gate = its columns of ``proj``; and each
+    request's new convolution history (its last taps - 1 rows of ``proj``) into ``state``."""
     n = o.shape[0]
     if y.shape != o.shape or weight.numel() != vdim:
         raise KernelError("delta_gated_norm: shapes do not agree")
     _check(load("delta_rule").ni_delta_gated_norm(
         _dev(o, "o", torch.float32), _dev(proj, "proj", torch.float32), _dev(weight, "weight", torch.float32), float(eps),
-        n, n_q_heads_kv, n_heads, dim, vdim, proj.shape[1], _dev(y, "y"), _code(y, "y"), _stream()), "delta_gated_norm")
+        n, n_seqs, n_q_heads_kv, n_heads, dim, vdim, taps, proj.shape[1], _dev(y, "y"), _code(y, "y"),
+        _dev(state, "state", torch.float32), state.shape[1], _dev(cu_q, "cu_q", torch.int32),
+        _dev(slots, "slots", torch.int32), _stream()), "delta_gated_norm")
 
 
 def latent_norm_write(proj, col0, rank, weight, eps, pages, positions, seq_of_token, block_table, page_size) -> None:

@@ -152,17 +152,28 @@ class ParallelBlock:
     def forward(self, h: torch.Tensor, delta, ctx, cache):
         if isinstance(delta, NormHandoff):
             delta = None                                   # the stream is up to date; this norm is computed here
-        x = self.mixer_norm.forward(h, delta)
+        rt, mixer, ffn = self.rt, self.mixer, self.feed_forward
         pending = []
-        for sub, args in ((self.mixer, (x, ctx, cache)), (self.feed_forward, (x, ctx))):
-            if sub is None:
-                continue
-            if getattr(sub, "adds_into_residual", False):
-                y = sub.forward(*args, residual=h)         # may add in place and return None
-            else:
-                y = sub.forward(*args)
-            if y is not None:
-                pending.append(y)
+        if (delta is None and rt.skinny(h.shape[0], self.hidden_size) and rt.fuses_norm(self.mixer_norm)
+                and hasattr(mixer, "project") and (ffn is None or hasattr(ffn, "project"))):
+            # a few rows: the norm runs inside each sublayer's first product; both read the stream before
+            # either adds into it (in the epilogue of its last product)
+            first = mixer.project(h, self.mixer_norm), (ffn.project(h, self.mixer_norm) if ffn is not None else None)
+            pending.append(mixer.finish(first[0], ctx, cache, residual=h))
+            if ffn is not None:
+                pending.append(ffn.finish(first[1], ctx, residual=h))
+            pending = [y for y in pending if y is not None]
+        else:
+            x = self.mixer_norm.forward(h, delta)
+            for sub, args in ((mixer, (x, ctx, cache)), (ffn, (x, ctx))):
+                if sub is None:
+                    continue
+                if getattr(sub, "adds_into_residual", False):
+                    y = sub.forward(*args, residual=h)         # may add in place and return None
+                else:
+                    y = sub.forward(*args)
+                if y is not None:
+                    pending.append(y)
         for y in pending:                                  # both sublayers have read x by now
             ops.residual_add(h, y)
         if self.input_dim > 0:

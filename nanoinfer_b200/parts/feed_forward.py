@@ -116,9 +116,17 @@ class PolyNorm(Part):
         return (self.w_up, self.w_down)
 
     def forward(self, x: torch.Tensor, ctx, residual=None):
+        return self.finish(self.rt.linear(x, self.w_up), ctx, residual=residual)
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        """up(norm(h)) with the norm inside the product (steps of a few rows)."""
+        z = self.rt.empty(h.shape[0], self.inter)
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_up, z, ops.STORE_BF16)
+        return z
+
+    def finish(self, z: torch.Tensor, ctx, residual=None):
         rt = self.rt
-        z = rt.linear(x, self.w_up)
-        act = rt.empty(x.shape[0], self.inter)
+        act = rt.empty(z.shape[0], self.inter)
         ops.polynorm(z, self.coef, self.eps, act)
         return rt.linear(act, self.w_down, residual=residual)
 

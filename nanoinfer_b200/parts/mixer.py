@@ -274,12 +274,20 @@ class LatentAttention(PagedAttendMixin, Part):
     graph_safe = "all"
 
     def forward(self, x: torch.Tensor, ctx, cache, residual=None):
+        return self.finish(self.rt.linear(x, self.w_in), ctx, cache, residual=residual)       # q | gate | dkv
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        """The fused input projection of norm(h), with the norm inside the product (steps of a few rows)."""
+        proj = self.rt.empty(h.shape[0], self.w_in.shape[0])
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_in, proj, ops.STORE_BF16)
+        return proj
+
+    def finish(self, proj: torch.Tensor, ctx, cache, residual=None):
         rt = self.rt
-        n = x.shape[0]
+        n = proj.shape[0]
         h, d, v, r = self.n_heads, self.qk_dim, self.value_dim, self.rank
         table = ctx.block_tables[cache.group]
         pages = cache.pages["latent"]                                  # [P, page_size, r]
-        proj = rt.linear(x, self.w_in)                                 # q | gate | dkv
         if self.own_latent:
             if not cache.writable:
                 raise ConfigError("latent attention: a layer with a latent of its own needs a cache of its own")

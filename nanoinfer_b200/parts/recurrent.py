@@ -74,11 +74,20 @@ class GatedDeltaRule(Part):
         return (self.w_in, self.w_o)
 
     def forward(self, x: torch.Tensor, ctx, cache, residual=None):
+        return self.finish(self.rt.linear(x, self.w_in, out_dtype=torch.float32), ctx, cache, residual=residual)
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        """The fused input projection of norm(h), with the norm inside the product (steps of a few rows): the first
+        half of forward for an arrangement that lets all its sublayers read the stream before any adds into it."""
+        proj = self.rt.empty(h.shape[0], self.w_in.shape[0], dtype=torch.float32)
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_in, proj, ops.STORE_F32)
+        return proj
+
+    def finish(self, proj: torch.Tensor, ctx, cache, residual=None):
         rt = self.rt
-        n = x.shape[0]
+        n = proj.shape[0]
         f32 = torch.float32
         g, h, d, v = self.G, self.H, self.D, self.V
-        proj = rt.linear(x, self.w_in, out_dtype=f32)
         qkv = rt.empty(n, self.channels, dtype=f32)
         gates = rt.empty(n, h, 2, dtype=f32)
         ops.delta_prepare(proj, self.conv_w, self.a_log, self.dt_bias, cache.state, ctx.seq_of_token, ctx.cu_q,
@@ -86,7 +95,7 @@ class GatedDeltaRule(Part):
         o = rt.empty(n, h * v, dtype=f32)
         ops.delta_recurrence(qkv, gates, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, g, h, d, v, o)
         y = rt.empty(n, h * v)
-        ops.delta_gated_norm(o, proj, self.norm_w, self.eps, g, h, d, v, y)
+        ops.delta_gated_norm(o, proj, self.norm_w, self.eps, g, h, d, v, y, cache.state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.taps)
         return rt.linear(y, self.w_o, residual=residual)
 
 

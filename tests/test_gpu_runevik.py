@@ -183,7 +183,7 @@ def test_delta_kernels_alone(G, H, D, V, taps):
         o = torch.empty(n, H * V, device=DEV)
         ops.delta_recurrence(qkv, gates, state, cu, slots, len(ids), G, H, D, V, o)
         y = torch.empty(n, H * V, device=DEV)
-        ops.delta_gated_norm(o, proj, norm_w.to(DEV), 1e-5, G, H, D, V, y)
+        ops.delta_gated_norm(o, proj, norm_w.to(DEV), 1e-5, G, H, D, V, y, state, cu, slots, len(ids), taps)
         at = 0
         for k in ids:
             got[k].append(y[at:at + step[k]].cpu())
