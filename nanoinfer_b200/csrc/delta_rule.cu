@@ -1,8 +1,8 @@
 // The gated delta rule: a recurrent token mixer with a matrix state per head.
 //
 // Per head (state S [D, V] in FP32, carried from token to token of a request):
-//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
-// with q and k unit vectors per head (q also times D^-1/2), g = exp(-exp(A_log) softplus(a + dt_bias))
+//     S *= decay;   e = beta * (v - k S);   S += outer(k, e);   y = q S        (k, q: rows of D; v, e, y: rows of V)
+// with q and k unit vectors per head (q also times D^-1/2), decay = exp(-exp(A_log) softplus(a + dt_bias))
 // and beta = sigmoid(b).  q, k and v first pass a short causal convolution over time per channel
 // and silu; the last taps-1 inputs of every channel are part of a request's state.
 //
@@ -115,7 +115,7 @@ __device__ __forceinline__ void delta_history(const float* __restrict__ proj, fl
 }
 
 // One warp per (request, head, a few value columns).  The rows of a column of S are cut into chunks of 8;
-// a lane keeps CHUNKS of them in registers and RG lanes share a column, so S^T k and S^T q are sums inside a
+// a lane keeps CHUNKS of them in registers and RG lanes share a column, so k S and q S are sums inside a
 // lane followed by log2(RG) shuffles.  The order of every sum is fixed by the chunk numbers alone (8 rows in
 // four interleaved chains, then a binary tree over the chunk index from its lowest bit up), so the two
 // layouts launched below - few lanes per column for single tokens, whose cost is reading and writing S in
@@ -240,7 +240,7 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
 #pragma unroll
             for (int c = 0; c < CHUNKS; c += 2 * w) part[c] += part[c + w];
         float dot = part[0];
-        // the lanes' partial sums of this token's S^T k and of the token before's S^T q travel together: two
+        // the lanes' partial sums of this token's k S and of the token before's q S travel together: two
         // independent shuffles per level instead of two trees one after the other
 #pragma unroll
         for (int off = COLS; off < 32; off <<= 1) {
@@ -267,7 +267,7 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
         for (int w = 1; w < CHUNKS; w <<= 1)
 #pragma unroll
             for (int c = 0; c < CHUNKS; c += 2 * w) part[c] += part[c + w];
-        o_pending = part[0];                   // summed over the lanes while the next token's S^T k is
+        o_pending = part[0];                   // summed over the lanes while the next token's k S is
         __syncwarp();                          // every lane has left this stage before a later fetch refills it
     }
 #pragma unroll

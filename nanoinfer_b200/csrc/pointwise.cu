@@ -89,8 +89,8 @@ NI_EXPORT int ni_add_normed(float* h, const void* y, int y_dtype, const float* w
     NI_RETURN_LAUNCH_STATUS();
 }
 
-// PolyNorm: out = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(v) = v / sqrt(mean(v^2) + eps)
-// over the row.  coef = {a, b, c, e} (FP32 on the device).
+// PolyNorm: out = c1 R(z) + c2 R(z * z) + c3 R(z * z * z) + c0: the first three powers of every value, each
+// power divided by its own root mean square over the row (eps under the root).  coef = {c1, c2, c3, c0}.
 template <typename T>
 __global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps,
                                 T* __restrict__ out, int n) {
@@ -187,7 +187,7 @@ NI_EXPORT int ni_polynorm(const void* z, int dtype, const float* coef, float eps
 }
 
 // out[t, j] = gelu_tanh(gate[t, j]) * table[tokens[t], first + j],  j < n; the table has `stride` columns.
-// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// The gate is the tanh form of GELU: z / 2 * (1 + tanh(c * (z + 0.044715 z^3))) with c = sqrt(2 / pi).
 template <typename T, typename TT>
 __global__ void gelu_table_gate_kernel(const T* __restrict__ gate, const int* __restrict__ tokens,
                                        const TT* __restrict__ table, T* __restrict__ out, int n_rows, int n,

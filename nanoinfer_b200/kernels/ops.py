@@ -390,7 +390,8 @@ def add_normed(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: floa
 
 
 def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
-    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps); coef = (a, b, c, e)
+    """out = c1 R(z) + c2 R(z * z) + c3 R(z * z * z) + c0 per row, where R divides a row by its root mean square
+    (eps under the root); coef = (c1, c2, c3, c0)
     float32 on the device; z and out [T, n] of one dtype."""
     if z.shape != out.shape or z.dtype != out.dtype or coef.numel() != 4:
         raise KernelError("polynorm: shapes or dtypes do not agree")
@@ -431,7 +432,8 @@ def delta_prepare(proj, conv_w, a_log, dt_bias, state, seq_of_token, cu_q, slots
 
 
 def delta_recurrence(qkv, gates, state, cu_q, slots, n_seqs, n_q_heads_kv, n_heads, dim, vdim, out) -> None:
-    """S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q for every token of every request, in order;
+    """Per head and token, in order: the state M [D, V] decays (M *= decay), the error e = beta * (v - k M) is
+    written back (M += outer(k, e)) and the token reads y = q M - for every token of every request;
     S float32 [H, D, V] at the start of each row of ``state``; out float32 [T, H V]."""
     f32 = torch.float32
     if out.shape != (qkv.shape[0], n_heads * vdim):

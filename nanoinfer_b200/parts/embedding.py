@@ -32,8 +32,8 @@ class TableEmbedding(Part):
 
 
 class SinusoidTableEmbedding(Part):
-    """Row ``id`` of a [vocab, hidden] table plus a sinusoidal position vector: entry 2i is
-    sin(p * base^(-2i / hidden)), entry 2i + 1 the cosine of the same angle (p = the token's position,
+    """Row ``id`` of a [vocab, hidden] table plus a sinusoidal position vector: the coordinates come in
+    pairs (sine, cosine) of the angle p * f_j, with f_j = base^(-2j / hidden) for pair j (p = the token's position,
     ``base`` from the spec's extra, 10000 by default).  Frequencies are computed once on the host in
     double precision and rounded to FP32; angles and the sum are FP32 on the device.
 

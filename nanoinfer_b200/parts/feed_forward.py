@@ -90,8 +90,9 @@ class SwiGLU(Part):
 
 
 class PolyNorm(Part):
-    """y = down(act(up(x))) with act(z) = a N(z) + b N(z^2) + c N(z^3) + e: powers element by element,
-    N(v) = v / sqrt(mean(v^2) + eps) over a token's feed-forward values, four learned numbers (a, b, c, e).
+    """y = down(act(up(x))) with act(z) = c1 R(z) + c2 R(z * z) + c3 R(z * z * z) + c0: the first three powers of
+    every value, each power divided by its own root mean square over the token's feed-forward values (eps under the
+    root), and four learned numbers, stored (c1, c2, c3, c0).
     The three means and the polynomial are FP32; ``eps`` comes in the spec's extra ("eps")."""
 
     kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in

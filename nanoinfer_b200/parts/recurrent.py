@@ -12,21 +12,22 @@ from .base import Part, StateNeed, WeightSlot
 
 
 class GatedDeltaRule(Part):
-    """The gated delta rule.  Per value head, with a matrix state S [dim, value_dim] in FP32:
+    """The gated delta rule.  Per value head, with a matrix state M [dim, value_dim] in FP32 - the token first predicts its own value from
+    the decayed state, writes the error back under its key, and reads with its query what the state then holds:
 
-        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+        M *= decay;   e = beta * (v - k M);   M += outer(k, e);   y = q M      (k, q rows of size dim; v, e, y of size value_dim)
 
     q and k (``num_kv_heads`` heads of ``head_dim``; value head h reads head h / (heads / kv heads)) and
     v (``num_heads`` heads of ``value_dim``) pass a short causal convolution over time per channel
     (``conv_taps`` taps, the last one the current token's, no bias) and silu; q and k are then unit
     vectors per head (1e-6 under the root), q also times head_dim^-1/2.  beta = sigmoid(W_b x), one per
-    head; g = exp(-exp(A_log) softplus(W_a x + dt_bias)), one per head.  Each head's o is divided by its
+    head; decay = exp(-exp(A_log) softplus(W_a x + dt_bias)), one per head.  Each head's y is divided by its
     root mean square (``norm_eps``), multiplied by a weight [value_dim] shared by the heads and by
     silu(W_g x), and leaves through W_o.
 
     All projections of x are ONE product (rows q | k | v | gate | b | a) whose results stay FP32;
     everything from there to the gated norm is FP32 on the device.  A request's state is one FP32 vector:
-    S of every head, then the last conv_taps - 1 inputs of every convolved channel.  A step's kernels
+    M of every head, then the last conv_taps - 1 inputs of every convolved channel.  A step's kernels
     run exactly once, so the state advances by exactly the step's tokens."""
 
     kernel_modules = ("delta_rule",)       # libraries of csrc that this part's kernels live in

@@ -25,7 +25,7 @@ def over_rms(x, eps):
 
 
 def sinusoid(positions, width, dtype):
-    """Entry 2i = sin(p * 10000^(-2i/width)), entry 2i+1 = cos of the same angle."""
+    """Pairs (sin, cos) of the angles p * f_j, f_j = 10000^(-2j / width), interleaved along the width."""
     out = torch.zeros(len(positions), width, dtype=dtype)
     p = torch.as_tensor(positions, dtype=dtype)[:, None]
     i = torch.arange((width + 1) // 2, dtype=dtype)[None, :]

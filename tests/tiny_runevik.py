@@ -29,7 +29,7 @@ R1 = {"architecture": "Runevik", "vocab": 300, "width": 96, "norm": {"eps": 1e-5
       "layers": [latent(3, 16, 24, 48, 0.31, 160), delta(2, 1, 24, 40, 3, 136), latent(2, 32, 16, 48, 0.2, 96, kv_from=0),
                  delta(3, 3, 16, 32, 2, 0)]}
 R2 = {"architecture": "Runevik", "vocab": 260, "width": 128, "norm": {"eps": 1e-6},
-      "layers": [delta(4, 2, 64, 64, 4, 192), latent(4, 32, 32, 64, 0.25, 192), latent(4, 16, 48, 64, 0.4, 0, kv_from=1)]}
+      "layers": [delta(6, 2, 64, 32, 4, 192), latent(4, 32, 32, 64, 0.25, 192), latent(4, 16, 48, 64, 0.4, 0, kv_from=1)]}
 R3 = {"architecture": "Runevik", "vocab": 200, "width": 64, "norm": {"eps": 1e-6}, "token_side": {"dim": 4},
       "layers": [delta(1, 1, 160, 32, 1, 64), latent(2, 16, 16, 128, 0.3, 64), delta(2, 2, 8, 8, 5, 0),
                  latent(1, 24, 40, 128, 0.15, 0, kv_from=1)]}
