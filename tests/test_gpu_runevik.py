@@ -150,15 +150,15 @@ def test_rowwise_kernels(dtype):
 
 
 @pytest.mark.parametrize("G, H, D, V, taps", [(1, 2, 24, 40, 3), (2, 2, 160, 33, 1), (2, 6, 64, 48, 4), (1, 1, 8, 8, 6),
-                                              (1, 1, 272, 16, 2)])
+                                              (1, 1, 272, 16, 2), (1, 2, 520, 8, 2)])
 def test_delta_kernels_alone(G, H, D, V, taps):
-    """Two requests whose tokens arrive in three steps of unequal portions (one of them shorter than the
-    convolution's history), in slots that are not in order; the plain mixer gets the same inputs through
-    projections that merely select columns."""
+    """Two requests whose tokens arrive in three steps of unequal portions (long ones, which take the kernel's
+    layout for long portions, and one shorter than the convolution's history), in slots that are not in order; the
+    plain mixer gets the same inputs through projections that merely select columns."""
     from nanoinfer_b200.kernels import ops
     g = torch.Generator().manual_seed(G + 10 * H + D)
     C, N = 2 * G * D + H * V, 2 * G * D + 2 * H * V + 2 * H
-    lens = {"a": 11, "b": 7}
+    lens = {"a": 43, "b": 9}
     inputs = {k: torch.randn(n, N, generator=g) for k, n in lens.items()}
     conv_w = torch.randn(C, taps, generator=g) * 0.6
     a_log, dt_bias = torch.randn(H, generator=g) - 2.0, torch.randn(H, generator=g)
@@ -169,7 +169,7 @@ def test_delta_kernels_alone(G, H, D, V, taps):
         state[s].zero_()
     got = {k: [] for k in lens}
     fed = {k: 0 for k in lens}
-    for step in ({"a": 5, "b": 1}, {"b": 4, "a": 1}, {"a": 5, "b": 2}):
+    for step in ({"a": 30, "b": 1}, {"b": 4, "a": 1}, {"a": 12, "b": 4}):
         ids = list(step)
         proj = torch.cat([inputs[k][fed[k]:fed[k] + step[k]] for k in ids]).to(DEV)
         n = proj.shape[0]
@@ -318,6 +318,23 @@ def test_latent_ranks_and_head_counts(tmp_path, dtype, heads, rank):
     want = {rid: plain.run(toks, plain.new_state())[0].float() for rid, toks in reqs.items()}
     steps = ru.mixed(reqs, max_live=2)
     _compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, label=f"latent {heads} x {rank}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_no_multiple_of_eight(tmp_path, dtype):
+    """A width of 100, a latent of 40, keys of 20, values of 12, a token input of 6, a vocabulary of 131: no fast
+    path takes these, and the rows of the caches and projections start on odd boundaries."""
+    raw = {"architecture": "Runevik", "vocab": 131, "width": 100, "norm": {"eps": 1e-5}, "token_side": {"dim": 6},
+           "layers": [tr.delta(3, 1, 20, 12, 3, 52), tr.latent(5, 12, 10, 40, 0.3, 36), tr.latent(2, 20, 14, 40, 0.25, 0, kv_from=1)]}
+    d = str(tmp_path / "m")
+    tr.write_model(d, raw, 33)
+    cfg, w = load_plain(d)
+    plain = PlainRunevik(cfg, w)
+    reqs = {"a": random_tokens(131, 39, 1), "b": random_tokens(131, 21, 2), "c": random_tokens(131, 2, 3)}
+    want = {rid: plain.run(toks, plain.new_state())[0].float() for rid, toks in reqs.items()}
+    for cut in (ru.whole, lambda r: ru.mixed(r, max_live=3)):
+        steps = cut(reqs)
+        _compare(ru.run_trace(_runner(d, dtype, steps), steps), want, dtype, label="odd sizes")
 
 
 # ---- whole models, cut in four ways ---------------------------------------------------------------------
