@@ -82,7 +82,10 @@ def _random_model(args) -> int:
         with open(args.config) as f:
             raw = json.load(f)
     if args.layers is not None:
-        raw = dict(raw, num_hidden_layers=args.layers)
+        if isinstance(raw.get("layers"), list):          # an architecture that lists its layers: the first ones
+            raw = dict(raw, layers=raw["layers"][:args.layers])
+        else:
+            raw = dict(raw, num_hidden_layers=args.layers)
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
     write_random_model(args.out, raw, args.seed, args.std, dtype)
     print(f"wrote {args.out}/config.json and model.safetensors (seed {args.seed})", file=sys.stderr)

@@ -73,6 +73,19 @@ def test_random_model_folder_loads(tmp_path):
     assert w["final.norm"].shape == () and w["l0.mix.q.conv"].shape == (160, 1) and w["side.embed"].shape == (200, 16)
 
 
+def test_command_line_writes_a_random_model(tmp_path):
+    import json
+    from nanoinfer_b200.cli import main
+    from nanoinfer_b200.config import load_config
+    from nanoinfer_b200.weights import load_weights
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(tr.R1))
+    assert main(["random-model", "--config", str(cfg_file), "--layers", "3", "--seed", "4", "--out", str(tmp_path / "m")]) == 0
+    cfg = load_config(str(tmp_path / "m"))
+    assert len(cfg.layers) == 3 and cfg.schedule[2].cache_of == 0
+    assert set(load_weights(str(tmp_path / "m"), cfg)) >= {"embed", "side.embed", "l2.mix.uk", "final.norm", "head"}
+
+
 def test_sinusoid_and_convolution_by_hand():
     pe = sinusoid([0, 3], 6, torch.float64)
     assert torch.allclose(pe[0], torch.tensor([0., 1., 0., 1., 0., 1.], dtype=torch.float64))
