@@ -130,6 +130,9 @@ class LayerSpec:
     (src/model/llama.cpp:324-379).
     arrangement "parallel":  x = norm1(h); h += mixer(x) + ffn(x) - one norm, read by both; such a
     layer has no ``ffn_norm`` and may have no feed-forward at all (both None).
+    arrangement "sandwich_norm":  h += post1(mixer(norm1(h))); h += post2(ffn(norm2(h))) - every sublayer's
+    output passes a norm of its own (``mixer_post_norm``, ``ffn_post_norm``) before it joins the stream;
+    the feed-forward with its two norms may be absent.
     ``extra`` carries the arrangement's own constants (for instance the width of a per-layer token
     input that it adds after the feed-forward).
     """
@@ -139,6 +142,8 @@ class LayerSpec:
     ffn_norm: Optional[NormSpec]
     arrangement: str = "pre_norm"
     extra: Tuple[Tuple[str, Any], ...] = ()
+    mixer_post_norm: Optional[NormSpec] = None
+    ffn_post_norm: Optional[NormSpec] = None
 
     def extra_dict(self) -> Dict[str, Any]:
         return dict(self.extra)
@@ -152,9 +157,13 @@ class LayerRun:
     weights are shared, every run has a cache of its own).
     ``cache_of``: index of an earlier *run* whose cache this run reads instead of
     writing one of its own; None = own cache.
+    ``stream_input``: row of the model's table of stream inputs (``ModelConfig.stream_inputs`` rows of
+    hidden_size, a weight of the model) that is added to every token's residual stream right before
+    this run; None = nothing.  A model that runs a span of layers several times marks each pass so.
     """
     layer: int
     cache_of: Optional[int] = None
+    stream_input: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -172,6 +181,7 @@ class ModelConfig:
     raw: Tuple[Tuple[str, Any], ...] = ()
     embedding: EmbeddingSpec = field(default_factory=EmbeddingSpec)
     head: HeadSpec = field(default_factory=HeadSpec)
+    stream_inputs: int = 0      # rows of the table that ``LayerRun.stream_input`` names (0: the model has none)
 
     @property
     def num_layers(self) -> int:
@@ -206,6 +216,9 @@ class ModelConfig:
                 if self.schedule[run.cache_of].cache_of is not None:
                     raise ConfigError(f"schedule[{r}].cache_of={run.cache_of} names a run "
                                       f"that has no cache of its own")
+            if run.stream_input is not None and not 0 <= run.stream_input < self.stream_inputs:
+                raise ConfigError(f"schedule[{r}].stream_input={run.stream_input} is outside the model's "
+                                  f"{self.stream_inputs} stream inputs")
 
 
 def require(raw: Dict[str, Any], key: str, typ) -> Any:

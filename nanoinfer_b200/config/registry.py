@@ -9,8 +9,9 @@ random-weights writer, engine, trace replay and command line all go through
 Adding an architecture = one ``register_architecture`` call with
   * ``parse_config(raw: dict) -> ModelConfig``: reads the architecture's own keys;
   * ``tensor_name(scope: tuple, slot: str) -> str``: the safetensors name of a part's
-    weight slot.  Scopes are ("embedding",), ("lm_head",), ("final_norm",) and
-    ("layer", i, "mixer" | "feed_forward" | "mixer_norm" | "ffn_norm" | "block") - "block" holds
+    weight slot.  Scopes are ("embedding",), ("lm_head",), ("final_norm",), ("stream_inputs",) (the
+    table of ``ModelConfig.stream_inputs``, if any) and ("layer", i, "mixer" | "feed_forward" |
+    "mixer_norm" | "ffn_norm" | "mixer_post_norm" | "ffn_post_norm" | "block") - "block" holds
     the weights of the arrangement itself, if its class has ``weight_slots``;
   * optionally ``ignored_tensors``: name patterns (fnmatch) of tensors that exporters of this
     architecture store beside the weights and that nothing reads (buffers such as a rotary

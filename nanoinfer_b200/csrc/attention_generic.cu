@@ -5,6 +5,8 @@
 // token list restricts the launch to some of the step's tokens (n_tokens = its length).
 // An optional slope per query head adds slope * (key position - query position) to the scaled
 // score: a position encoding that acts on the scores instead of rotating queries and keys.
+// An optional cap bounds the scaled score smoothly: s <- cap * tanh(s / cap) (cap = 0: none), FP32, before
+// the bias and the softmax.
 //
 // The result of a token depends only on its own keys and their order, never on how the
 // step was cut or what else is in the batch, so this kernel is the FP32 path's attention
@@ -27,7 +29,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ block_table, int bt_stride,
                                          int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                                          int page_size, int window, float scale,
-                                         const float* __restrict__ head_slopes) {
+                                         const float* __restrict__ head_slopes, float score_cap) {
     const int warps_per_block = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * n_q_heads) return;
@@ -62,7 +64,9 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
             if (dim < head_dim) dot += qr[r] * ni_to_float(krow[dim]);
         }
         dot = ni_warp_sum(dot);
-        const float s = dot * scale + slope * (float)(j - pos);
+        float s = dot * scale;
+        if (score_cap > 0.f) s = score_cap * tanhf(s / score_cap);
+        s += slope * (float)(j - pos);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
         const float p = expf(s - m_new);
@@ -88,7 +92,7 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
                                    const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
                                    int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                                    int page_size, int window, float scale, const float* head_slopes,
-                                   cudaStream_t stream) {
+                                   float score_cap, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0)
         return NI_ERR_BAD_ARGUMENT;
@@ -101,7 +105,7 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
     attention_generic_kernel<T, R><<<(int)blocks, warps * 32, 0, stream>>>(                         \
         (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_list, positions,         \
         seq_of_token,                                                                               \
-        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes)
+        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes, score_cap)
 #define LAUNCH(T)                          \
     do {                                   \
         if (head_dim <= 256) LAUNCH_R(T, 8); \

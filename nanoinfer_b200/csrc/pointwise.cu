@@ -217,3 +217,93 @@ NI_EXPORT int ni_gelu_table_gate(const void* gate, int dtype, const int* tokens,
 #undef LAUNCH
     NI_RETURN_LAUNCH_STATUS();
 }
+
+// h[t, :] += row[:] for every token (a learned vector that joins the stream); FP32.
+template <typename T>
+__global__ void add_row_kernel(float* __restrict__ h, const T* __restrict__ row, long long n, int d) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) h[i] += ni_to_float(row[i % d]);
+}
+
+NI_EXPORT int ni_add_row(float* h, const void* row, int row_dtype, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return NI_OK;
+    if (d <= 0) return NI_ERR_BAD_ARGUMENT;
+    const long long n = (long long)n_rows * d, blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+    if (row_dtype == NI_DTYPE_F32) add_row_kernel<float><<<(int)blocks, 256, 0, stream>>>(h, (const float*)row, n, d);
+    else if (row_dtype == NI_DTYPE_BF16)
+        add_row_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(h, (const __nv_bfloat16*)row, n, d);
+    else return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// x *= factor, element by element (FP32: logits).
+__global__ void scale_f32_kernel(float* __restrict__ x, float factor, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= factor;
+}
+
+NI_EXPORT int ni_scale_f32(float* x, float factor, long long n, cudaStream_t stream) {
+    if (n <= 0) return NI_OK;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+    scale_f32_kernel<<<(int)blocks, 256, 0, stream>>>(x, factor, n);
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// A gated unit with capped arguments: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(slope * g) * (u + shift); gate_up = [gate | up] along the columns.
+template <typename T>
+__global__ void capped_glu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long n, int inter,
+                                  float limit, float slope, float shift) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / inter;
+    const int c = (int)(i - t * inter);
+    const T* row = gate_up + (size_t)t * 2 * inter;
+    const float g = fminf(ni_to_float(row[c]), limit);
+    const float u = fminf(fmaxf(ni_to_float(row[inter + c]), -limit), limit);
+    out[i] = ni_from_float<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
+}
+
+NI_EXPORT int ni_capped_glu(const void* gate_up, void* out, int dtype, int n_rows, int inter, float limit, float slope,
+                            float shift, cudaStream_t stream) {
+    if (n_rows <= 0) return NI_OK;
+    if (inter <= 0) return NI_ERR_BAD_ARGUMENT;
+    const long long n = (long long)n_rows * inter, blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
+    if (dtype == NI_DTYPE_F32)
+        capped_glu_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, n, inter, limit, slope, shift);
+    else if (dtype == NI_DTYPE_BF16)
+        capped_glu_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n,
+                                                                         inter, limit, slope, shift);
+    else return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
+// out[t, :] = table[tokens[t], :] * scale as FP32 (an id out of range writes zeros).
+template <typename T>
+__global__ void embedding_scaled_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float scale,
+                                        float* __restrict__ out, int d, int vocab) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    const bool ok = tok >= 0 && tok < vocab;
+    const T* row = table + (size_t)(ok ? tok : 0) * d;
+    float* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? ni_to_float(row[i]) * scale : 0.f;
+}
+
+NI_EXPORT int ni_embedding_scaled(const int* tokens, const void* table, int table_dtype, float scale, float* out,
+                                  int n_tokens, int d, int vocab, cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (d <= 0 || vocab <= 0) return NI_ERR_BAD_ARGUMENT;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == NI_DTYPE_F32)
+        embedding_scaled_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, scale, out, d, vocab);
+    else if (table_dtype == NI_DTYPE_BF16)
+        embedding_scaled_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, scale,
+                                                                                out, d, vocab);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}

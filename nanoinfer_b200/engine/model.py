@@ -9,6 +9,7 @@ import torch
 
 from ..config import registry
 from ..config.model_config import ModelConfig
+from ..kernels import ops
 from ..weights.plan import tensor_plan
 
 
@@ -30,6 +31,10 @@ class DecoderModel:
             self.blocks.append(cls(layer, d, lambda what, i=i: by_scope.get(("layer", i, what), {}), rt))
             if hasattr(self.blocks[-1], "bind_embedding"):     # a block that reads a table the embedding owns
                 self.blocks[-1].bind_embedding(self.embedding)
+        # vectors that join the stream before marked runs (LayerRun.stream_input): FP32 rows on the device
+        self.stream_inputs = None
+        if config.stream_inputs > 0:
+            self.stream_inputs = rt.gain(by_scope[("stream_inputs",)]["weight"])
         self.final_norm = registry.part("norm", config.final_norm.kind)(
             config.final_norm, d, by_scope.get(("final_norm",), {}), rt)
         head = config.head_spec()
@@ -78,6 +83,12 @@ class DecoderModel:
             self.embedding.forward(ctx.tokens, h)
         delta = None
         for r, run in enumerate(cfg.schedule):
+            if run.stream_input is not None:
+                # a vector joins the stream before this run; what the block before left pending goes in first
+                if delta is not None and not isinstance(delta, ops.NormHandoff):
+                    ops.residual_add(h, delta)
+                delta = None
+                ops.add_row(h, self.stream_inputs[run.stream_input])
             ctx.read_after, ctx.norm_after = self._read_after[r], self._norm_after[r]
             delta = self.blocks[run.layer].forward(h, delta, ctx, caches[r])
         ctx.read_after, ctx.norm_after = (), None

@@ -210,7 +210,8 @@ class ModelRunner:
         # libraries that only some parts use (a part names them in ``kernel_modules``): built together, now
         extra = sorted({m for b in self.model.blocks for p in (b, getattr(b, "mixer", None), getattr(b, "feed_forward", None))
                         for m in getattr(p, "kernel_modules", ())}
-                       | set(getattr(self.model.embedding, "kernel_modules", ())))
+                       | set(getattr(self.model.embedding, "kernel_modules", ()))
+                       | set(getattr(self.model.head, "kernel_modules", ())))
         if extra:
             ops.preload(extra)
 
@@ -221,18 +222,27 @@ class ModelRunner:
         self.caches: List[Optional[CacheView]] = [None] * len(needs)
         self._state_runs: List[int] = []
         for r, need in enumerate(needs):
-            if isinstance(need, (PagedKVNeed, PagedNeed)):
-                key = (planes_of(need), need.window)
-                if key not in group_keys:
-                    group_keys.append(key)
-                    kv = isinstance(need, PagedKVNeed)
-                    group_specs.append(GroupSpec(need.num_kv_heads if kv else 0, need.head_dim if kv else 0, need.window))
-                self.caches[r] = CacheView(group=group_keys.index(key))
-            elif isinstance(need, StateNeed):
-                self.caches[r] = CacheView()
-                self._state_runs.append(r)
-            elif need is not None:
-                raise StepError(f"run {r}: unknown cache need {need!r}")
+            # a mixer may need several things (pages and a state): it then names them in a tuple
+            for one in (need if isinstance(need, tuple) else (need,)):
+                if one is None:
+                    continue
+                if self.caches[r] is None:
+                    self.caches[r] = CacheView()
+                if isinstance(one, (PagedKVNeed, PagedNeed)):
+                    if self.caches[r].group >= 0:
+                        raise StepError(f"run {r}: more than one paged cache need")
+                    key = (planes_of(one), one.window)
+                    if key not in group_keys:
+                        group_keys.append(key)
+                        kv = isinstance(one, PagedKVNeed)
+                        group_specs.append(GroupSpec(one.num_kv_heads if kv else 0, one.head_dim if kv else 0, one.window))
+                    self.caches[r].group = group_keys.index(key)
+                elif isinstance(one, StateNeed):
+                    if r in self._state_runs:
+                        raise StepError(f"run {r}: more than one state need")
+                    self._state_runs.append(r)
+                else:
+                    raise StepError(f"run {r}: unknown cache need {one!r}")
         if not group_specs:
             group_specs.append(GroupSpec(0, 0, None))  # bookkeeping of lengths only
         pages_per_group = self._pages_per_group(num_pages, group_specs, page_size, max_requests, max_portion_tokens)
@@ -245,14 +255,15 @@ class ModelRunner:
         rt = self.rt
         for r, need in enumerate(needs):
             view = self.caches[r]
-            if isinstance(need, (PagedKVNeed, PagedNeed)):
-                n_pages = pages_per_group[view.group]
-                for name, row in planes_of(need):
-                    shape = (n_pages,) + tuple(row[:-1]) + (page_size, row[-1])
-                    view.pages[name] = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
-            elif isinstance(need, StateNeed):
-                dt = rt.dtype if need.dtype == "compute" else getattr(torch, need.dtype)
-                view.state = torch.zeros((max_requests,) + tuple(need.shape), dtype=dt, device=rt.device)
+            for one in (need if isinstance(need, tuple) else (need,)):
+                if isinstance(one, (PagedKVNeed, PagedNeed)):
+                    n_pages = pages_per_group[view.group]
+                    for name, row in planes_of(one):
+                        shape = (n_pages,) + tuple(row[:-1]) + (page_size, row[-1])
+                        view.pages[name] = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+                elif isinstance(one, StateNeed):
+                    dt = rt.dtype if one.dtype == "compute" else getattr(torch, one.dtype)
+                    view.state = torch.zeros((max_requests,) + tuple(one.shape), dtype=dt, device=rt.device)
         for r, run in enumerate(config.schedule):
             if run.cache_of is not None:
                 src = self.caches[run.cache_of]

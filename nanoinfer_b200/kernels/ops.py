@@ -34,7 +34,7 @@ _SIGNATURES = {
         "ni_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_generic": {
-        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _F, _P],
     },
     "gemm_f32": {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
@@ -46,6 +46,21 @@ _SIGNATURES = {
         "ni_add_normed": [_P, _P, _I, _P, _F, _I, _I, _P],
         "ni_polynorm": [_P, _I, _P, _F, _P, _I, _I, _P],
         "ni_gelu_table_gate": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+        "ni_add_row": [_P, _P, _I, _I, _I, _P],
+        "ni_embedding_scaled": [_P, _P, _I, _F, _P, _I, _I, _I, _P],
+        "ni_scale_f32": [_P, _F, _LL, _P],
+        "ni_capped_glu": [_P, _P, _I, _I, _I, _F, _F, _F, _P],
+    },
+    "conv_attention": {
+        "ni_conv_qk_prepare": [_P, _I, _I, _P, _P, _P, _F, _P, _LL, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P,
+                               _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    },
+    "routed": {
+        "ni_route": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "ni_route_layout": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+        "ni_expert_gemm": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ni_expert_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ni_route_combine": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     },
     "delta_rule": {
         "ni_delta_prepare": [_P, _P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
@@ -313,10 +328,12 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                       block_table: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, window: Optional[int], scale: float,
-                      token_list: Optional[torch.Tensor] = None, head_slopes: Optional[torch.Tensor] = None) -> None:
+                      token_list: Optional[torch.Tensor] = None, head_slopes: Optional[torch.Tensor] = None,
+                      score_cap: float = 0.0) -> None:
     """The plain attention kernel (any dtype, any head size up to 512).  ``token_list``
     int32 [n] restricts it to those tokens of the step.  ``head_slopes`` float32 [Hq] adds
-    slope[h] * (key position - query position) to the scaled scores of head h."""
+    slope[h] * (key position - query position) to the scaled scores of head h.  ``score_cap`` c > 0
+    bounds the scaled scores: s <- c * tanh(s / c)."""
     if head_slopes is not None and head_slopes.numel() != n_q_heads:
         raise KernelError("attention: one slope per query head")
     n = q.shape[0]
@@ -333,7 +350,8 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], n if token_list is None else token_list.numel(), n_q_heads, n_kv_heads, head_dim, page_size,
         int(window) if window else 0, float(scale),
-        _dev(head_slopes, "head_slopes", torch.float32) if head_slopes is not None else None, _stream()), "attention_generic")
+        _dev(head_slopes, "head_slopes", torch.float32) if head_slopes is not None else None, float(score_cap),
+        _stream()), "attention_generic")
 
 
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -476,6 +494,151 @@ def head_gate(x, proj, col0, n_heads, vdim) -> None:
         raise KernelError("head_gate: shapes or dtypes do not agree")
     _check(load("latent").ni_head_gate(_dev(x, "x"), _code(x, "x"), _dev(proj, "proj"), proj.shape[1], int(col0), n,
                                        n_heads, vdim, _stream()), "head_gate")
+
+
+def embedding_scaled(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    """out[t, :] = float32(table[tokens[t], :]) * scale;  tokens int32 [T], out float32 [T, d]."""
+    n, d = out.shape
+    if tokens.numel() != n or table.shape[1] != d:
+        raise KernelError("embedding_scaled: shapes do not agree")
+    _check(load("pointwise").ni_embedding_scaled(_dev(tokens, "tokens", torch.int32), _dev(table, "table"),
+                                                 _code(table, "table"), float(scale), _dev(out, "out", torch.float32),
+                                                 n, d, table.shape[0], _stream()), "embedding_scaled")
+
+
+def add_row(h: torch.Tensor, row: torch.Tensor) -> None:
+    """h[t, :] += row for every t; h float32 [T, d], row [d] (float32 or bfloat16)."""
+    n, d = h.shape
+    if row.numel() != d:
+        raise KernelError("add_row: the row must have the width of h")
+    _check(load("pointwise").ni_add_row(_dev(h, "h", torch.float32), _dev(row, "row"), _code(row, "row"), n, d, _stream()),
+           "add_row")
+
+
+def scale_f32(x: torch.Tensor, factor: float) -> None:
+    """x *= factor in place; x float32."""
+    _check(load("pointwise").ni_scale_f32(_dev(x, "x", torch.float32), float(factor), x.numel(), _stream()), "scale_f32")
+
+
+def capped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float) -> None:
+    """out = g * sigmoid(slope * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit);
+    gate_up = [gate | up] [T, 2I], out [T, I], one dtype."""
+    n, inter = out.shape
+    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
+        raise KernelError("capped_glu: gate_up must be [T, 2I] of out's dtype")
+    _check(load("pointwise").ni_capped_glu(_dev(gate_up, "gate_up"), _dev(out, "out"), _code(out, "out"), n, inter,
+                                           float(limit), float(slope), float(shift), _stream()), "capped_glu")
+
+
+def conv_qk_prepare(proj, conv_w, q_gain, k_gain, eps, state, positions, seq_of_token, cu_q, slots, n_seqs, block_table,
+                    inv_freq, q_out, k_pages, v_pages, n_heads, n_kv_heads, head_dim, rotary_dim, taps, page_size) -> None:
+    """From the fused projection ``proj`` [T, ld] (columns: the queries' channels, the keys' channels, then whatever
+    else): causal convolution over time per channel (``conv_w`` float32 [C, taps], the last tap the token's own;
+    what lies before a portion comes from the request's history in ``state`` float32 [slots, (taps - 1) C]), RMS
+    norm per head (``q_gain`` / ``k_gain`` float32 [head_dim]), rotation of adjacent pairs of the first
+    ``rotary_dim`` dimensions; queries -> q_out [T, H hd], keys -> k_pages, the keys' convolution output as it is ->
+    v_pages (pages [P, Hkv, page_size, hd]; None: nothing is written); then the history moves on."""
+    n = proj.shape[0]
+    c = (n_heads + n_kv_heads) * head_dim
+    write = k_pages is not None
+    f32, i32 = torch.float32, torch.int32
+    if proj.shape[1] < c or q_out.shape != (n, n_heads * head_dim) or conv_w.shape != (c, taps):
+        raise KernelError("conv_qk_prepare: shapes do not agree")
+    if q_out.dtype != proj.dtype or (write and (k_pages.dtype != proj.dtype or v_pages.dtype != proj.dtype)):
+        raise KernelError("conv_qk_prepare: all activations must share one dtype")
+    if write and (tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim) or v_pages.shape != k_pages.shape):
+        raise KernelError("conv_qk_prepare: pages must be [P, Hkv, page_size, head_dim]")
+    if state.shape[1] != (taps - 1) * c or q_gain.numel() != head_dim or k_gain.numel() != head_dim:
+        raise KernelError("conv_qk_prepare: the state or a gain has another size")
+    if rotary_dim > 0 and inv_freq.numel() != rotary_dim // 2:
+        raise KernelError("conv_qk_prepare: inv_freq must have rotary_dim / 2 entries")
+    _check(load("conv_attention").ni_conv_qk_prepare(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.shape[1], _dev(conv_w, "conv_w", f32), _dev(q_gain, "q_gain", f32),
+        _dev(k_gain, "k_gain", f32), float(eps), _dev(state, "state", f32), state.shape[1],
+        _dev(positions, "positions", i32), _dev(seq_of_token, "seq_of_token", i32), _dev(cu_q, "cu_q", i32),
+        _dev(slots, "slots", i32), _dev(block_table, "block_table", i32), block_table.shape[1],
+        _dev(inv_freq, "inv_freq", f32), _dev(q_out, "q_out"), _dev(k_pages, "k_pages") if write else None,
+        _dev(v_pages, "v_pages") if write else None, n, n_seqs, n_heads, n_kv_heads, head_dim, rotary_dim, taps,
+        page_size, _stream()), "conv_qk_prepare")
+
+
+ROUTE_MAX_EXPERTS = 256      # what the routing kernel keeps in shared memory per token
+
+
+def route(x, w_router, bias, ids, weights, counts, n_real, top, renormalize=False) -> None:
+    """Per token: scores = softmax(w_router x) (float32; w_router float32 [E, d]); the ``top`` experts with the
+    largest score + bias (``bias`` float32 [E] or None) -> ids int32 [T, top], their scores -> weights float32
+    [T, top] (divided by their sum if ``renormalize``).  ``counts`` int32 [n_real] (or None) receives how many
+    tokens chose each of the first ``n_real`` experts (added to what it holds)."""
+    n, d = x.shape
+    e = w_router.shape[0]
+    if w_router.shape != (e, d) or ids.shape != (n, top) or weights.shape != (n, top) or (bias is not None and bias.numel() != e):
+        raise KernelError("route: shapes do not agree")
+    if e > ROUTE_MAX_EXPERTS:
+        raise KernelError(f"route: {e} experts, more than the kernel's {ROUTE_MAX_EXPERTS}")
+    _check(load("routed").ni_route(_dev(x, "x"), _code(x, "x"), _dev(w_router, "w_router", torch.float32),
+                                   _dev(bias, "bias", torch.float32) if bias is not None else None,
+                                   _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
+                                   _dev(counts, "counts", torch.int32) if counts is not None else None, n, d, e, n_real, top,
+                                   1 if renormalize else 0, _stream()), "route")
+
+
+def route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of_row, n_real) -> None:
+    """Lay the (token, choice) pairs out expert by expert: offsets / tile_first int32 [n_real + 1] (first row and
+    first 64-row tile of each expert's stretch), row_of_pair int32 [T top] (-1 for pairs of identity experts),
+    token_of_row int32 [T top]; counts comes from route() and is left zero, cursor int32 [n_real] is scratch."""
+    n, top = ids.shape
+    i32 = torch.int32
+    if offsets.numel() < n_real + 1 or tile_first.numel() < n_real + 1 or row_of_pair.numel() < n * top or token_of_row.numel() < n * top:
+        raise KernelError("route_layout: a buffer is too small")
+    _check(load("routed").ni_route_layout(_dev(ids, "ids", i32), _dev(counts, "counts", i32), _dev(offsets, "offsets", i32),
+                                          _dev(tile_first, "tile_first", i32), _dev(cursor, "cursor", i32),
+                                          _dev(row_of_pair, "row_of_pair", i32), _dev(token_of_row, "token_of_row", i32),
+                                          n * top, top, n_real, _stream()), "route_layout")
+
+
+def expert_gemm(a, token_of_row, w, out, offsets, tile_first, n_pairs, act: bool) -> None:
+    """out[row] = a[row] . w[e]^T for the rows of every expert e's stretch (``token_of_row`` given: a[token of the
+    row]); w [E, N, K], or with ``act`` [E, 2N, K] (gate rows, then up rows) and out = silu(gate) * up.  Each output
+    element is one ascending chain of FP32 fused multiply-adds."""
+    e, wn, k = w.shape
+    n = wn // 2 if act else wn
+    if a.shape[1] != k or out.shape[1] != n or out.shape[0] < n_pairs or a.dtype != w.dtype or out.dtype != w.dtype:
+        raise KernelError("expert_gemm: shapes or dtypes do not agree")
+    _check(load("routed").ni_expert_gemm(_dev(a, "a"), _code(a, "a"),
+                                         _dev(token_of_row, "token_of_row", torch.int32) if token_of_row is not None else None,
+                                         _dev(w, "w"), _dev(out, "out"), _dev(offsets, "offsets", torch.int32),
+                                         _dev(tile_first, "tile_first", torch.int32), n_pairs, e, n, k, 1 if act else 0,
+                                         _stream()), "expert_gemm")
+
+
+EXPERT_ROWS_MAX_PAIRS = 64      # (token, choice) pairs up to which a step takes the kernel with one warp per output
+
+
+def expert_rows(a, w, out, ids, gather: bool, act: bool) -> None:
+    """A few rows, bfloat16: out[p] = a[p or p / top] . w[ids[p]]^T for every pair p of a real expert (others are
+    skipped), one warp per output; ``act`` as in expert_gemm.  K must be a multiple of 8."""
+    e, wn, k = w.shape
+    n = wn // 2 if act else wn
+    n_pairs, top = ids.numel(), ids.shape[1]
+    bf = torch.bfloat16
+    if a.shape[1] != k or out.shape != (n_pairs, n) or a.shape[0] != (n_pairs // top if gather else n_pairs):
+        raise KernelError("expert_rows: shapes do not agree")
+    _check(load("routed").ni_expert_rows(_dev(a, "a", bf), _dev(w, "w", bf), _dev(out, "out", bf), _dev(ids, "ids", torch.int32),
+                                         n_pairs, top, 1 if gather else 0, e, n, k, 1 if act else 0, _stream()), "expert_rows")
+
+
+def route_combine(z, x, ids, weights, row_of_pair, y, n_real) -> None:
+    """y[t] = sum_j weights[t, j] * (z[row of pair (t, j)] for a real expert, x[t] for an identity expert), in the
+    order of the choices, float32; row_of_pair None: pair p's row is p."""
+    n, top = ids.shape
+    d = x.shape[1]
+    if y.shape != (n, d) or z.shape[1] != d or z.dtype != x.dtype:
+        raise KernelError("route_combine: shapes or dtypes do not agree")
+    _check(load("routed").ni_route_combine(_dev(z, "z"), _dev(x, "x"), _code(x, "x"), _dev(ids, "ids", torch.int32),
+                                           _dev(weights, "weights", torch.float32),
+                                           _dev(row_of_pair, "row_of_pair", torch.int32) if row_of_pair is not None else None,
+                                           _dev(y, "y", torch.float32), n, d, top, n_real, _stream()), "route_combine")
 
 
 GEMV_MAX_ROWS = 16      # what the skinny kernels take

@@ -195,5 +195,64 @@ class ParallelBlock:
         ops.add_normed(h, y, self.input_gain, self.input_eps)
 
 
+class SandwichNormBlock:
+    """h += post1(mixer(norm1(h)));  h += post2(ffn(norm2(h))): every sublayer reads the stream through a
+    norm and its output passes a second norm of its own before it joins the stream (a layer may have no
+    feed-forward, then it has neither of that sublayer's norms).  The stream and both post norms'
+    statistics are FP32; a sublayer hands its output over in FP32 where its last product can."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    def __init__(self, layer_spec, hidden_size: int, weights_of, rt) -> None:
+        self.rt, self.hidden_size = rt, hidden_size
+
+        def norm(spec, what):
+            return part("norm", spec.kind)(spec, hidden_size, weights_of(what), rt)
+
+        if layer_spec.mixer_post_norm is None:
+            raise ValueError("a sandwich layer needs a norm on its mixer's output")
+        self.mixer_norm = norm(layer_spec.mixer_norm, "mixer_norm")
+        self.mixer_post = norm(layer_spec.mixer_post_norm, "mixer_post_norm")
+        self.mixer = part("mixer", layer_spec.mixer.kind)(layer_spec.mixer, hidden_size, weights_of("mixer"), rt)
+        self.feed_forward = self.ffn_norm = self.ffn_post = None
+        if layer_spec.feed_forward is not None:
+            if layer_spec.ffn_norm is None or layer_spec.ffn_post_norm is None:
+                raise ValueError("a sandwich layer's feed-forward needs both of its norms")
+            self.ffn_norm = norm(layer_spec.ffn_norm, "ffn_norm")
+            self.ffn_post = norm(layer_spec.ffn_post_norm, "ffn_post_norm")
+            self.feed_forward = part("feed_forward", layer_spec.feed_forward.kind)(
+                layer_spec.feed_forward, hidden_size, weights_of("feed_forward"), rt)
+        for post in (self.mixer_post, self.ffn_post):
+            if post is not None and not rt.fuses_norm(post):
+                raise ValueError("a sandwich layer's output norms must be RMS norms with a gain per coordinate")
+
+    def weights_in_order(self) -> tuple:
+        ffn = self.feed_forward
+        return tuple(getattr(self.mixer, "weights_in_order", tuple)()) + \
+            (tuple(getattr(ffn, "weights_in_order", tuple)()) if ffn is not None else ())
+
+    def first_norm(self):
+        return None
+
+    def _sublayer(self, sub, norm, post, h, args) -> None:
+        rt = self.rt
+        if (rt.skinny(h.shape[0], self.hidden_size) and rt.fuses_norm(norm) and hasattr(sub, "project")):
+            y = sub.finish(sub.project(h, norm), *args)      # a few rows: the norm runs inside the first product
+        else:
+            y = sub.forward(norm.forward(h, None), *args)
+        ops.add_normed(h, y, post.gain, post.eps)
+
+    def forward(self, h: torch.Tensor, delta, ctx, cache):
+        if isinstance(delta, NormHandoff):
+            delta = None                                   # the stream is up to date; this norm is computed here
+        if delta is not None:
+            ops.residual_add(h, delta)
+        self._sublayer(self.mixer, self.mixer_norm, self.mixer_post, h, (ctx, cache))
+        if self.feed_forward is not None:
+            self._sublayer(self.feed_forward, self.ffn_norm, self.ffn_post, h, (ctx,))
+        return None
+
+
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)
+register_part("arrangement", "sandwich_norm", SandwichNormBlock, replace=True)
 register_part("arrangement", "parallel", ParallelBlock, replace=True)

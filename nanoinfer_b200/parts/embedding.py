@@ -14,7 +14,9 @@ class TableEmbedding(Part):
     (src/op/kernels/cuda/embedding_kernel.cu:7-31; the reference keeps the stream in the weights'
     precision, here it is FP32 from the first row on).
 
-    ``table`` is the matrix on the device in the compute dtype; a tied head reads it too."""
+    ``table`` is the matrix on the device in the compute dtype; a tied head reads it too.
+    ``scale`` in the spec's extra (1 by default) multiplies every row as it enters the stream; the
+    table itself, which a tied head reads, stays as stored."""
 
     graph_safe = "all"
 
@@ -25,10 +27,16 @@ class TableEmbedding(Part):
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
         self.table = rt.weight(weights["weight"])
+        self.scale = float(spec.extra_dict().get("scale", 1.0))
+        if self.scale != 1.0:
+            self.kernel_modules = ("pointwise",)      # the library of csrc that the scaled kernel lives in
 
     def forward(self, tokens, h) -> None:
         """tokens int32 [T] on the device; fills h [T, hidden] FP32."""
-        ops.embedding(tokens, self.table, h)
+        if self.scale != 1.0:
+            ops.embedding_scaled(tokens, self.table, self.scale, h)
+        else:
+            ops.embedding(tokens, self.table, h)
 
 
 class SinusoidTableEmbedding(Part):

@@ -5,6 +5,7 @@ from typing import Dict
 
 import torch
 
+from ..config.model_config import ConfigError
 from ..config.registry import register_part
 from ..kernels import ops
 from .base import Part, WeightSlot
@@ -132,5 +133,142 @@ class PolyNorm(Part):
         return rt.linear(act, self.w_down, residual=residual)
 
 
+class CappedGLU(Part):
+    """A gated unit whose arguments are capped: g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit),
+    y = W_down (g * sigmoid(gate_slope * g) * (u + up_shift)); ``limit``, ``gate_slope`` and ``up_shift`` come in
+    the spec's extra.  Gate and up are one product; the output leaves in FP32 (the arrangement norms it)."""
+
+    kernel_modules = ("pointwise",)       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = False
+    graph_safe = "all"
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        i = spec.intermediate_size
+        return {"gate": WeightSlot((i, hidden_size)), "up": WeightSlot((i, hidden_size)),
+                "down": WeightSlot((hidden_size, i))}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        e = spec.extra_dict()
+        self.inter = spec.intermediate_size
+        self.limit = float(e["limit"])
+        self.slope, self.shift = float(e.get("gate_slope", 1.0)), float(e.get("up_shift", 0.0))
+        self.w_gate_up = rt.weight(torch.cat([weights["gate"], weights["up"]], dim=0))
+        self.w_down = rt.weight(weights["down"])
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_gate_up, self.w_down)
+
+    def forward(self, x: torch.Tensor, ctx):
+        return self.finish(self.rt.linear(x, self.w_gate_up), ctx)
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        """gate | up of norm(h) with the norm inside the product (steps of a few rows)."""
+        z = self.rt.empty(h.shape[0], 2 * self.inter)
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_gate_up, z, ops.STORE_BF16)
+        return z
+
+    def finish(self, gate_up: torch.Tensor, ctx):
+        rt = self.rt
+        act = rt.empty(gate_up.shape[0], self.inter)
+        ops.capped_glu(gate_up, act, self.limit, self.slope, self.shift)
+        return rt.linear(act, self.w_down, out_dtype=torch.float32)
+
+
+class RoutedExperts(Part):
+    """A routed feed-forward: ``experts`` small gated units W_down (silu(W_gate x) * (W_up x)) without biases, of
+    which every token uses ``top``, plus ``identity_experts`` experts whose output is x itself (they have no
+    weights and are numbered after the real ones).  Router: s = softmax(W_router x) over all experts, FP32; the
+    chosen ones are those with the largest s + correction (``choice_bias``), their weights are s, divided by
+    their sum only if ``renormalize``; the output is the weighted sum, FP32.
+
+    The experts' matrices are stacked ([E, 2F, d] gate rows then up rows, and [E, d, F]).  Steps of a few
+    (token, choice) pairs in bfloat16 stream each pair's expert with one warp per output; otherwise the pairs
+    are laid out expert by expert on the device and one launch per product multiplies every stretch with its
+    expert's matrix (csrc/routed.cu).  Nothing is decided on the host, so a step can be captured."""
+
+    kernel_modules = ("routed",)       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = False
+    graph_safe = "all"
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return int(e["experts"]), int(e.get("identity_experts", 0)), int(e["top"]), spec.intermediate_size
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        n_real, n_id, top, f = RoutedExperts._dims(spec)
+        slots = {"router": WeightSlot((n_real + n_id, hidden_size))}
+        if spec.extra_dict().get("choice_bias", False):
+            slots["correction"] = WeightSlot((n_real + n_id,))
+        for j in range(n_real):
+            slots[f"e{j}.gate"] = WeightSlot((f, hidden_size))
+            slots[f"e{j}.up"] = WeightSlot((f, hidden_size))
+            slots[f"e{j}.down"] = WeightSlot((hidden_size, f))
+        return slots
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        n_real, n_id, top, f = self._dims(spec)
+        if n_real + n_id > ops.ROUTE_MAX_EXPERTS or not 0 < top <= n_real + n_id:
+            raise ConfigError(f"routed experts: {n_real} + {n_id} experts (at most {ops.ROUTE_MAX_EXPERTS}) with top {top} "
+                              f"is not supported")
+        self.n_real, self.n_all, self.top, self.inter = n_real, n_real + n_id, top, f
+        self.renormalize = bool(spec.extra_dict().get("renormalize", False))
+        self.w_router = rt.gain(weights["router"])                  # the router runs in FP32
+        self.bias = rt.gain(weights["correction"]) if "correction" in weights else None
+        if n_real > 0:
+            self.w_gate_up = rt.weight(torch.stack([torch.cat([weights[f"e{j}.gate"], weights[f"e{j}.up"]], dim=0)
+                                                    for j in range(n_real)]))
+            self.w_down = rt.weight(torch.stack([weights[f"e{j}.down"] for j in range(n_real)]))
+        else:
+            self.w_gate_up = self.w_down = None
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_gate_up, self.w_down) if self.n_real > 0 else ()
+
+    def forward(self, x: torch.Tensor, ctx):
+        rt = self.rt
+        n, d = x.shape
+        top, n_real, f = self.top, self.n_real, self.inter
+        pairs = n * top
+        i32 = torch.int32
+        ids = rt.empty(n, top, dtype=i32)
+        weights = rt.empty(n, top, dtype=torch.float32)
+        y = rt.empty(n, d, dtype=torch.float32)
+        few = (rt.dtype == torch.bfloat16 and pairs <= ops.EXPERT_ROWS_MAX_PAIRS and d % 8 == 0 and f % 8 == 0)
+        if n_real == 0:
+            ops.route(x, self.w_router, self.bias, ids, weights, None, 0, top, self.renormalize)
+            ops.route_combine(x, x, ids, weights, None, y, 0)
+            return y
+        if few:
+            ops.route(x, self.w_router, self.bias, ids, weights, None, n_real, top, self.renormalize)
+            act = rt.empty(pairs, f)
+            ops.expert_rows(x, self.w_gate_up, act, ids, gather=True, act=True)
+            z = rt.empty(pairs, d)
+            ops.expert_rows(act, self.w_down, z, ids, gather=False, act=False)
+            ops.route_combine(z, x, ids, weights, None, y, n_real)
+            return y
+        counts = rt.workspace("routed_counts", ops.ROUTE_MAX_EXPERTS, i32, zero=True)
+        ops.route(x, self.w_router, self.bias, ids, weights, counts, n_real, top, self.renormalize)
+        meta = rt.empty(3 * (n_real + 1) + 2 * pairs, dtype=i32)
+        offsets, tile_first, cursor = (meta[i * (n_real + 1):(i + 1) * (n_real + 1)] for i in range(3))
+        row_of_pair = meta[3 * (n_real + 1):3 * (n_real + 1) + pairs]
+        token_of_row = meta[3 * (n_real + 1) + pairs:]
+        ops.route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of_row, n_real)
+        act = rt.empty(pairs, f)
+        ops.expert_gemm(x, token_of_row, self.w_gate_up, act, offsets, tile_first, pairs, act=True)
+        z = rt.empty(pairs, d)
+        ops.expert_gemm(act, None, self.w_down, z, offsets, tile_first, pairs, act=False)
+        ops.route_combine(z, x, ids, weights, row_of_pair, y, n_real)
+        return y
+
+
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "capped_glu", CappedGLU, replace=True)
+register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
 register_part("feed_forward", "polynorm", PolyNorm, replace=True)

@@ -12,7 +12,8 @@ class LinearHead(Part):
     """Final norm of the wanted rows, then the product with a [vocab, hidden] matrix
     (src/model/llama.cpp:381-389).  A tied head stores no matrix: it is handed the embedding's
     table as its "weight" (one device copy; the reference uploads the shared matrix twice,
-    src/model/llama.cpp:576-578,652-657)."""
+    src/model/llama.cpp:576-578,652-657).  ``logit_scale`` in the spec's extra (1 by default)
+    multiplies the FP32 logits."""
 
     graph_safe = "all"
 
@@ -24,6 +25,9 @@ class LinearHead(Part):
         super().__init__(spec, hidden_size, weights, rt)
         self.vocab_size = spec.vocab_size
         self.weight = rt.weight(weights["weight"])     # already on the device when it is the embedding's table
+        self.logit_scale = float(spec.extra_dict().get("logit_scale", 1.0))
+        if self.logit_scale != 1.0:
+            self.kernel_modules = ("pointwise",)      # the library of csrc that the scaling kernel lives in
 
     def weights_in_order(self) -> tuple:
         return (self.weight,)
@@ -31,6 +35,12 @@ class LinearHead(Part):
     def forward(self, h, delta, norm, ctx) -> torch.Tensor:
         """h FP32 [T, hidden] with ``delta`` still to be added (or None); returns FP32 logits
         [ctx.n_logit_rows, vocab] for rows ctx.logit_rows."""
+        logits = self._logits(h, delta, norm, ctx)
+        if self.logit_scale != 1.0 and logits.numel() > 0:
+            ops.scale_f32(logits, self.logit_scale)
+        return logits
+
+    def _logits(self, h, delta, norm, ctx) -> torch.Tensor:
         rt = self.rt
         if ctx.n_logit_rows == 0:
             return rt.empty(0, self.vocab_size, dtype=torch.float32)

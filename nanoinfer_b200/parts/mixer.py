@@ -9,7 +9,7 @@ import torch
 from ..config.model_config import ConfigError
 from ..config.registry import part, register_part
 from ..kernels import ops
-from .base import PagedKVNeed, PagedNeed, Part, StepPlan, WeightSlot
+from .base import PagedKVNeed, PagedNeed, Part, StateNeed, StepPlan, WeightSlot
 
 
 class PagedAttendMixin:
@@ -59,11 +59,12 @@ class PagedAttendMixin:
         common = (self.n_heads, self.n_kv, self.head_dim, rt.page_size, self.window, self.scale)
         n = q.shape[0]
         slopes = getattr(self.position, "head_slopes", None)
-        if rt.dtype != torch.bfloat16 or slopes is not None:
-            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)):
-            # the plain kernel takes both; the tensor-core kernels know rotations only
+        cap = float(getattr(self, "score_cap", 0.0))       # > 0: scores are bounded by cap * tanh(s / cap)
+        if rt.dtype != torch.bfloat16 or slopes is not None or cap > 0.0:
+            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)), or
+            # capped scores: the plain kernel takes all of them
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                  table, *common, head_slopes=slopes)
+                                  table, *common, head_slopes=slopes, score_cap=cap)
             return
         decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
         prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM
@@ -302,6 +303,102 @@ class LatentAttention(PagedAttendMixin, Part):
         return rt.linear(out, self.w_o, residual=residual)
 
 
+class ConvKeyAttention(PagedAttendMixin, Part):
+    """Grouped-query attention whose queries and keys pass a short causal convolution, and whose values are
+    the keys.  With x the mixer's input:
+
+        q, k = conv(W_q x), conv(W_k x)         per channel over time, ``conv_taps`` taps, the last one the token's
+                                                own, zeros before the sequence's start, no bias
+        v    = k                                as it leaves the convolution: there is no value projection
+        q, k <- RMS norm per head               one weight [head_dim] for all query heads, one for all key heads
+        q, k <- the position encoding           (rotary: adjacent pairs of the first ``rotary_dim`` dimensions)
+        s    = (q . k) softmax_scale;  s <- cap tanh(s / cap) if ``score_cap`` > 0;  causal softmax;  sum p v
+        head h's result times sigmoid(W_g x)_h; then W_o
+
+    W_q, W_k and W_g are one product; convolution, norm, rotation and the cache write are one kernel
+    (csrc/conv_attention.cu), all of it FP32 inside.  Per token the cache holds the finished key and the value;
+    per request a state row holds the last conv_taps - 1 projected rows (FP32), so a portion may be cut
+    anywhere.  ``forward`` returns the output projection in FP32 (the arrangement norms it)."""
+
+    kernel_modules = ("conv_attention", "latent")       # libraries of csrc that this part's kernels live in
+
+    adds_into_residual = False
+    graph_safe = "all"
+
+    @staticmethod
+    def _dims(spec):
+        e = spec.extra_dict()
+        return spec.num_heads, spec.num_kv_heads, spec.head_dim, int(e.get("conv_taps", 1))
+
+    @staticmethod
+    def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
+        h, g, d, taps = ConvKeyAttention._dims(spec)
+        return {"q": WeightSlot((h * d, hidden_size)), "k": WeightSlot((g * d, hidden_size)),
+                "q.norm": WeightSlot((d,), init="ones"), "k.norm": WeightSlot((d,), init="ones"),
+                "q.conv": WeightSlot((h * d, taps)), "k.conv": WeightSlot((g * d, taps)),
+                "g": WeightSlot((h, hidden_size)), "o": WeightSlot((hidden_size, h * d))}
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        Part.__init__(self, spec, hidden_size, weights, rt)
+        h, g, d, taps = self._dims(spec)
+        if h <= 0 or g <= 0 or h % g:
+            raise ConfigError("conv-key attention: heads must be a positive multiple of kv_heads")
+        if not 0 < d <= 512 or taps < 1:
+            raise ConfigError(f"conv-key attention: head size {d} (1 to 512) or {taps} taps is not supported")
+        e = spec.extra_dict()
+        self.n_heads, self.n_kv, self.head_dim, self.taps = h, g, d, taps
+        self.window = None
+        self.scale = float(spec.softmax_scale)
+        self.score_cap = float(e.get("score_cap", 0.0))
+        self.eps = float(e.get("norm_eps", 1e-6))
+        self.position = part("position", spec.position.kind)(spec.position, hidden_size, {}, rt)
+        if self.position.rotary_dim > d or (self.position.rotary_dim > 0 and not self.position.interleaved):
+            raise ConfigError("conv-key attention rotates adjacent pairs of at most head_dim dimensions")
+        if getattr(self.position, "head_slopes", None) is not None:
+            raise ConfigError("conv-key attention takes no position encoding that acts on the scores")
+        self.channels = (h + g) * d
+        self.w_in = rt.weight(torch.cat([weights["q"], weights["k"], weights["g"]], dim=0))      # q | k | gate
+        self.w_o = rt.weight(weights["o"])
+        self.conv_w = rt.gain(torch.cat([weights["q.conv"], weights["k.conv"]], dim=0))
+        self.q_gain, self.k_gain = rt.gain(weights["q.norm"]), rt.gain(weights["k.norm"])
+        self._no_state = torch.zeros((1, 0), dtype=torch.float32, device=rt.device)
+
+    def cache_need(self):
+        pages = PagedKVNeed(self.n_kv, self.head_dim, None)
+        if self.taps == 1:
+            return pages
+        return (pages, StateNeed(((self.taps - 1) * self.channels,), "float32"))
+
+    def weights_in_order(self) -> tuple:
+        return (self.w_in, self.w_o)
+
+    def forward(self, x: torch.Tensor, ctx, cache):
+        return self.finish(self.rt.linear(x, self.w_in), ctx, cache)
+
+    def project(self, h: torch.Tensor, norm) -> torch.Tensor:
+        """The fused input projection of norm(h), with the norm inside the product (steps of a few rows)."""
+        proj = self.rt.empty(h.shape[0], self.w_in.shape[0])
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_in, proj, ops.STORE_BF16)
+        return proj
+
+    def finish(self, proj: torch.Tensor, ctx, cache):
+        rt = self.rt
+        n = proj.shape[0]
+        h, g, d = self.n_heads, self.n_kv, self.head_dim
+        table = ctx.block_tables[cache.group]
+        if not cache.writable:
+            raise ConfigError("conv-key attention needs a cache of its own")
+        q = rt.empty(n, h * d)
+        state = cache.state if cache.state is not None else self._no_state
+        ops.conv_qk_prepare(proj, self.conv_w, self.q_gain, self.k_gain, self.eps, state, ctx.positions,
+                            ctx.seq_of_token, ctx.cu_q, ctx.slots, ctx.n_seqs, table, self.position.inv_freq, q,
+                            cache.k_pages, cache.v_pages, h, g, d, self.position.rotary_dim, self.taps, rt.page_size)
+        att = rt.empty(n, h * d)
+        self._attend(q, cache, att, ctx, table)
+        ops.head_gate(att, proj, self.channels, h, d)
+        return rt.linear(att, self.w_o, out_dtype=torch.float32)
+
+
 def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
     """Rows i and i + rot/2 of every head become rows 2i and 2i + 1; rows beyond rot stay."""
     out_dim, in_dim = w.shape
@@ -312,3 +409,4 @@ def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: in
 
 register_part("mixer", "attention", PagedAttention, replace=True)
 register_part("mixer", "latent_attention", LatentAttention, replace=True)
+register_part("mixer", "conv_key_attention", ConvKeyAttention, replace=True)

@@ -62,6 +62,18 @@ class RotaryEncoding(Part):
             rope_inverse_frequencies(spec.rotary_dim, spec.theta, spec.scaling)).to(rt.device)
 
 
+class RotaryEncodingExact(RotaryEncoding):
+    """Rotary encoding whose frequencies theta^(-2i / rotary_dim) are computed in double precision and rounded
+    once to FP32 (no rescaling rule); angles stay FP32 products position * frequency on the device."""
+
+    def __init__(self, spec, hidden_size, weights, rt) -> None:
+        super().__init__(spec, hidden_size, weights, rt)
+        if spec.scaling is not None:
+            raise ConfigError("the exact rotary encoding has no rescaling rule")
+        i = np.arange(spec.rotary_dim // 2, dtype=np.float64)
+        self.inv_freq = torch.from_numpy(np.power(float(spec.theta), -2.0 * i / spec.rotary_dim).astype(np.float32)).to(rt.device)
+
+
 class NoEncoding(Part):
     """No position encoding: queries and keys are used as projected."""
     head_slopes = None
@@ -74,4 +86,5 @@ class NoEncoding(Part):
 
 
 register_part("position", "rope", RotaryEncoding, replace=True)
+register_part("position", "rope_exact", RotaryEncodingExact, replace=True)
 register_part("position", "none", NoEncoding, replace=True)

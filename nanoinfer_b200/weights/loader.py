@@ -15,7 +15,7 @@ from typing import Dict, List
 
 import torch
 
-from ..config.model_config import ModelConfig
+from ..config.model_config import ConfigError, ModelConfig
 from . import safetensors_io as sio
 from .plan import tensor_plan
 
@@ -55,7 +55,10 @@ def check_tensors(model_dir: str, config: ModelConfig, found: Dict[str, tuple]) 
     allowed_extra = set()
     if config.head_spec().tied:
         # a tied model may still store its output projection; it is not read
-        allowed_extra.add(arch.tensor_name(("lm_head",), "weight"))
+        try:
+            allowed_extra.add(arch.tensor_name(("lm_head",), "weight"))
+        except ConfigError:
+            pass                      # an architecture whose output is always the embedding's table names none
     unexpected = [n for n in found if n not in plan and n not in allowed_extra
                   and not any(fnmatchcase(n, pat) for pat in arch.ignored_tensors)]
     wrong = [(n, plan[n].shape, found[n]) for n in plan if n in found and tuple(found[n]) != plan[n].shape]

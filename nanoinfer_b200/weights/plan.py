@@ -11,6 +11,7 @@ from typing import List, Tuple
 
 from ..config import registry
 from ..config.model_config import ModelConfig
+from ..parts.base import WeightSlot
 
 
 @dataclass(frozen=True)
@@ -45,9 +46,14 @@ def tensor_plan(config: ModelConfig) -> List[PlannedTensor]:
         if layer.feed_forward is not None:
             add(("layer", i, "feed_forward"),
                 registry.part("feed_forward", layer.feed_forward.kind).weight_slots(layer.feed_forward, d))
+        for what, spec in (("mixer_post_norm", layer.mixer_post_norm), ("ffn_post_norm", layer.ffn_post_norm)):
+            if spec is not None:                              # norms on a sublayer's output
+                add(("layer", i, what), registry.part("norm", spec.kind).weight_slots(spec, d))
         block = registry.part("arrangement", layer.arrangement)
         if hasattr(block, "weight_slots"):                    # weights of the arrangement itself
             add(("layer", i, "block"), block.weight_slots(layer, d))
+    if config.stream_inputs > 0:                              # vectors added to the stream before marked runs
+        add(("stream_inputs",), {"weight": WeightSlot((config.stream_inputs, d))})
     add(("final_norm",),
         registry.part("norm", config.final_norm.kind).weight_slots(config.final_norm, d))
     head = config.head_spec()
