@@ -108,14 +108,17 @@ __device__ __forceinline__ void dec_warm(const unsigned char* p, unsigned long l
 // every split writes its partial result into the shared memory of the cluster's first block, one
 // cluster barrier, and that block merges them in split order - no scratch in global memory, no
 // fence, no ticket.
-template <int HD, int SEG, bool CL>
+// CAP: the scaled scores are bounded smoothly, s <- cap * tanh(s / cap), before the softmax.  The kernel is then
+// handed scale_log2e = 2 log2(e) scale / cap and cap_l2 = cap log2(e): with x = exp2(raw * scale_log2e),
+// cap_l2 - 2 cap_l2 / (x + 1) is the capped score in the exponent's base.
+template <int HD, int SEG, bool CL, bool CAP>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                         const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ token_list, const int* __restrict__ positions,
                         const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                         int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
-                        float scale_log2e, int n_splits, float* __restrict__ scratch,
+                        float scale_log2e, float cap_l2, int n_splits, float* __restrict__ scratch,
                         int* __restrict__ tickets, const unsigned char* __restrict__ warm_a, unsigned long long warm_a_bytes,
                         const unsigned char* __restrict__ warm_b, unsigned long long warm_b_bytes) {
     // Weights that the kernels after this one will read (the caller's hint, up to two regions): asked
@@ -257,7 +260,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const bool ok = w0 + 8 * j + 2 * t + (e & 1) < seg_keys;
-                    s[j][e] = ok ? s[j][e] * scale_log2e : -INFINITY;
+                    float sc = s[j][e] * scale_log2e;
+                    if (CAP) sc = fmaf(-2.f * cap_l2, __fdividef(1.f, dec_exp2(sc) + 1.f), cap_l2);
+                    s[j][e] = ok ? sc : -INFINITY;
                 }
                 mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
                 mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
@@ -811,22 +816,22 @@ NI_EXPORT int ni_attention_decode_balanced(const void* q, const void* k_pages, c
     }
 }
 
-template <int HD, int SEG, bool CL>
+template <int HD, int SEG, bool CL, bool CAP>
 static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_list,
                          int n_items, const int* positions, const int* seq_of_token, const int* block_table,
                          int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
-                         float scale_log2e, int n_splits, float* scratch, int* tickets, const void* warm_a,
+                         float scale_log2e, float cap_l2, int n_splits, float* scratch, int* tickets, const void* warm_a,
                          unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
                          cudaStream_t stream) {
     const size_t kv_smem = (size_t)(16 + 4 * SEG) * HD * sizeof(__nv_bfloat16);
     const size_t smem = kv_smem + (CL ? (size_t)n_splits * (n_q_heads / n_kv_heads) * (HD + 2) * sizeof(float) : 0);
     static size_t configured = 0;
     if (configured < smem) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, SEG, CL>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, SEG, CL, CAP>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         if (CL) {   // clusters of 9 to 16 blocks (a lone request's many splits) are beyond the portable size
-            e = cudaFuncSetAttribute(attention_decode_kernel<HD, SEG, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            e = cudaFuncSetAttribute(attention_decode_kernel<HD, SEG, CL, CAP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             if (e != cudaSuccess) return (int)e;
         }
         configured = smem;
@@ -849,10 +854,10 @@ static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pa
     // 1.13).  Started after its predecessor, the cluster variant wins (0.804; batch 4: 0.801 -> 0.773).
     cfg.attrs = CL ? attr + 1 : attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, SEG, CL>, (const __nv_bfloat16*)q,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, SEG, CL, CAP>, (const __nv_bfloat16*)q,
                                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
                                        (__nv_bfloat16*)out, token_list, positions, seq_of_token, block_table,
-                                       bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e, n_splits,
+                                       bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e, cap_l2, n_splits,
                                        scratch, tickets, (const unsigned char*)warm_a, warm_a_bytes,
                                        (const unsigned char*)warm_b, warm_b_bytes);
     return e == cudaSuccess ? NI_OK : (int)e;
@@ -870,31 +875,30 @@ template <int HD, int SEG>
 static int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_list,
                          int n_items, const int* positions, const int* seq_of_token, const int* block_table,
                          int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
-                         float scale_log2e, int n_splits, float* scratch, int* tickets, const void* warm_a,
+                         float scale_log2e, float cap_l2, int n_splits, float* scratch, int* tickets, const void* warm_a,
                          unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
                          cudaStream_t stream) {
     const size_t slot_bytes = (size_t)n_splits * (n_q_heads / n_kv_heads) * (HD + 2) * sizeof(float);
     const bool few_blocks = (long long)n_items * n_kv_heads * n_splits <= 2LL * ni_sm_count() && slot_bytes <= 65536;
     if (dec_cluster_merge && n_splits >= 2 && ((n_splits <= 8 && slot_bytes <= DEC_CLUSTER_SLOT_BYTES) || (n_splits <= 16 && few_blocks)))
-        return launch_decode_cl<HD, SEG, true>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
-                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                               scale_log2e, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b,
-                                               warm_b_bytes, stream);
-    return launch_decode_cl<HD, SEG, false>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
-                                            block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                            scale_log2e, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b,
-                                            warm_b_bytes, stream);
+#define NI_DEC_GO(CL, CAP)                                                                                          \
+    launch_decode_cl<HD, SEG, CL, CAP>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,          \
+                                       block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e,   \
+                                       cap_l2, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b, warm_b_bytes, stream)
+        return cap_l2 > 0.f ? NI_DEC_GO(true, true) : NI_DEC_GO(true, false);
+    return cap_l2 > 0.f ? NI_DEC_GO(false, true) : NI_DEC_GO(false, false);
+#undef NI_DEC_GO
 }
 
 // Scratch floats needed: n_items * n_q_heads * n_splits * (head_dim + 2); tickets: n_items * n_kv_heads
 // ints, zero before the first launch (the kernel leaves them zero).
 NI_EXPORT int ni_attention_decode_fresh_keys() { return DEC_FRESH_KEYS; }
 
-NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out,
+static int decode_dispatch(const void* q, const void* k_pages, const void* v_pages, void* out,
                                   const int* token_list, int n_items, const int* positions,
                                   const int* seq_of_token, const int* block_table, int bt_stride,
                                   int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
-                                  float scale, int n_splits, float* scratch, int* tickets,
+                                  float scale, float score_cap, int n_splits, float* scratch, int* tickets,
                                   const void* warm_a, long long warm_a_bytes, const void* warm_b,
                                   long long warm_b_bytes, cudaStream_t stream) {
     if (n_items <= 0) return NI_OK;
@@ -904,7 +908,9 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
         n_splits > 65535 || n_kv_heads > 65535)
         return NI_ERR_BAD_ARGUMENT;
     if (n_q_heads / n_kv_heads > 16) return NI_ERR_UNSUPPORTED_SIZE;
-    const float scale_log2e = scale * 1.4426950408889634f;
+    // capped scores (score_cap > 0): see the kernel's note on what the two numbers are then
+    const float scale_log2e = score_cap > 0.f ? 2.f * 1.4426950408889634f * scale / score_cap : scale * 1.4426950408889634f;
+    const float cap_l2 = score_cap > 0.f ? score_cap * 1.4426950408889634f : 0.f;
     switch (head_dim) {
         case 64:
             // while all blocks fit the GPU at 3 per SM: fat blocks with 128-key buffers; beyond that
@@ -913,19 +919,45 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
             if ((long long)n_items * n_kv_heads * n_splits <= 3LL * ni_sm_count())
                 return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                              scale_log2e, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
+                                              scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
                                               (unsigned long long)warm_b_bytes, stream);
             return launch_decode<64, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                          scale_log2e, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
+                                          scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
                                               (unsigned long long)warm_b_bytes, stream);
         case 128:
             return launch_decode<128, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                            block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                           scale_log2e, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
+                                           scale_log2e, cap_l2, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
                                               (unsigned long long)warm_b_bytes, stream);
         default: return NI_ERR_UNSUPPORTED_SIZE;
     }
+}
+
+NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                  const int* token_list, int n_items, const int* positions,
+                                  const int* seq_of_token, const int* block_table, int bt_stride,
+                                  int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
+                                  float scale, int n_splits, float* scratch, int* tickets,
+                                  const void* warm_a, long long warm_a_bytes, const void* warm_b,
+                                  long long warm_b_bytes, cudaStream_t stream) {
+    return decode_dispatch(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table, bt_stride,
+                           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, 0.f, n_splits, scratch, tickets,
+                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, stream);
+}
+
+// The same with the scaled scores bounded by score_cap * tanh(s / score_cap) (score_cap > 0).
+NI_EXPORT int ni_attention_decode_capped(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                         const int* token_list, int n_items, const int* positions,
+                                         const int* seq_of_token, const int* block_table, int bt_stride,
+                                         int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
+                                         float scale, float score_cap, int n_splits, float* scratch, int* tickets,
+                                         const void* warm_a, long long warm_a_bytes, const void* warm_b,
+                                         long long warm_b_bytes, cudaStream_t stream) {
+    if (!(score_cap > 0.f)) return NI_ERR_BAD_ARGUMENT;
+    return decode_dispatch(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table, bt_stride,
+                           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, score_cap, n_splits, scratch, tickets,
+                           warm_a, warm_a_bytes, warm_b, warm_b_bytes, stream);
 }
 
 // ---- the variant that allocates nothing (see attention_decode_noalloc.h) ----------------------

@@ -58,14 +58,18 @@ template <int HD> __device__ __forceinline__ int sw(int row, int chunk) {
     return row * HD + ((chunk ^ (row & MASK)) << 3);
 }
 
-template <int HD>
+// CAP: the scaled scores are bounded smoothly, s <- cap * tanh(s / cap), before mask and softmax.  The kernel is
+// then handed scale_log2e = 2 log2(e) scale / cap and cap_l2 = cap log2(e): with x = exp2(raw * scale_log2e),
+// cap_l2 * tanh(.) = cap_l2 - 2 cap_l2 / (x + 1) is the capped score in the exponent's base; its error is a few
+// units in the last place of cap_l2, far below the rounding of the probabilities to bfloat16.
+template <int HD, bool CAP>
 __global__ void __launch_bounds__(PF_WARPS * 32)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                          const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                          const int* __restrict__ block_table, int bt_stride, int n_q_heads,
-                         int n_kv_heads, int page_size, int window, float scale_log2e) {
+                         int n_kv_heads, int page_size, int window, float scale_log2e, float cap_l2) {
     constexpr int CH = HD / 8;        // 16-byte chunks per row
     constexpr int KS = HD / 16;       // k-steps over the head size
     constexpr int NT_O = HD / 8;      // output column tiles
@@ -168,6 +172,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                     pf_mma(s[2 * jp + 1], qa[ks], b[2], b[3]);
                 }
             }
+            if (CAP) {
+#pragma unroll
+                for (int j = 0; j < PF_BN / 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        s[j][e] = fmaf(-2.f * cap_l2, __fdividef(1.f, pf_exp2(s[j][e] * scale_log2e) + 1.f), cap_l2);
+                }
+            }
+            const float sl = CAP ? 1.0f : scale_log2e;     // capped scores are in the exponent's base already
             // Scores stay unscaled; the scale rides in the exponent's FMA: p = 2^(s * scale - m).
             // Only tiles that touch the diagonal or a window's edge need the mask.
             const bool need_mask = k0 + PF_BN - 1 > warp_first || (window > 0 && k0 < warp_last - window + 1);
@@ -195,7 +208,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             // m0, m1: running maxima of the SCALED scores (the scale is positive)
-            const float mn0 = fmaxf(m0, mx0 * scale_log2e), mn1 = fmaxf(m1, mx1 * scale_log2e);
+            const float mn0 = fmaxf(m0, mx0 * sl), mn1 = fmaxf(m1, mx1 * sl);
             // a row with no visible key so far keeps max = -inf: use 0 as the reference point
             const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
             const bool rescale = mn0 != m0 || mn1 != m1;
@@ -205,8 +218,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             uint32_t pa[PF_BN / 16][4];
 #pragma unroll
             for (int j = 0; j < PF_BN / 8; ++j) {
-                const float p0 = pf_exp2(fmaf(s[j][0], scale_log2e, -ref0)), p1 = pf_exp2(fmaf(s[j][1], scale_log2e, -ref0));
-                const float p2 = pf_exp2(fmaf(s[j][2], scale_log2e, -ref1)), p3 = pf_exp2(fmaf(s[j][3], scale_log2e, -ref1));
+                const float p0 = pf_exp2(fmaf(s[j][0], sl, -ref0)), p1 = pf_exp2(fmaf(s[j][1], sl, -ref0));
+                const float p2 = pf_exp2(fmaf(s[j][2], sl, -ref1)), p3 = pf_exp2(fmaf(s[j][3], sl, -ref1));
                 rs0 += p0 + p1;
                 rs1 += p2 + p3;
                 const __nv_bfloat162 r01 = __floats2bfloat162_rn(p0, p1), r23 = __floats2bfloat162_rn(p2, p3);
@@ -254,15 +267,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     }
 }
 
-template <int HD> static int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
+template <int HD, bool CAP> static int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                                             const int* tile_seq, const int* tile_row0, int n_tiles,
                                             const int* cu_q, const int* kv_len, const int* block_table,
                                             int bt_stride, int n_q_heads, int n_kv_heads, int page_size,
-                                            int window, float scale_log2e, cudaStream_t stream) {
+                                            int window, float scale_log2e, float cap_l2, cudaStream_t stream) {
     const size_t smem = (size_t)(PF_BM + 4 * PF_BN) * HD * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, CAP>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -270,10 +283,10 @@ template <int HD> static int launch_prefill(const void* q, const void* k_pages, 
     const long long blocks = (long long)n_tiles * n_q_heads;
     if (blocks > 0x7fffffffLL) return NI_ERR_UNSUPPORTED_SIZE;
     dim3 grid((unsigned)blocks);
-    attention_prefill_kernel<HD><<<grid, PF_WARPS * 32, smem, stream>>>(
+    attention_prefill_kernel<HD, CAP><<<grid, PF_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
         (__nv_bfloat16*)out, tile_seq, tile_row0, cu_q, kv_len, block_table, bt_stride, n_q_heads,
-        n_kv_heads, page_size, window, scale_log2e);
+        n_kv_heads, page_size, window, scale_log2e, cap_l2);
     NI_RETURN_LAUNCH_STATUS();
 }
 
@@ -283,13 +296,18 @@ NI_EXPORT int ni_attention_prefill(const void* q, const void* k_pages, const voi
                                    const int* tile_seq, const int* tile_row0, int n_tiles, const int* cu_q,
                                    const int* kv_len, const int* block_table, int bt_stride, int n_q_heads,
                                    int n_kv_heads, int head_dim, int page_size, int window, float scale,
-                                   cudaStream_t stream) {
+                                   float score_cap, cudaStream_t stream) {
     if (n_tiles <= 0) return NI_OK;
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0)
         return NI_ERR_BAD_ARGUMENT;
-    const float sl = scale * 1.4426950408889634f;
-#define GO(HD) return launch_prefill<HD>(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len, \
-                                         block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, sl, stream)
+    const bool cap = score_cap > 0.f;
+    const float sl = cap ? 2.f * 1.4426950408889634f * scale / score_cap : scale * 1.4426950408889634f;
+    const float cl = cap ? score_cap * 1.4426950408889634f : 0.f;
+#define GO(HD)                                                                                                         \
+    return cap ? launch_prefill<HD, true>(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len,       \
+                                          block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, sl, cl, stream) \
+               : launch_prefill<HD, false>(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len,      \
+                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window, sl, cl, stream)
     switch (head_dim) {
         case 16: GO(16);
         case 32: GO(32);

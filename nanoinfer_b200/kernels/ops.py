@@ -86,6 +86,7 @@ _SIGNATURES = {
     },
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
+        "ni_attention_decode_capped": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_balanced": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_fresh_keys": [],
         "ni_attention_decode_set_cluster_merge": [_I],
@@ -93,7 +94,7 @@ _SIGNATURES = {
         "ni_attention_decode_noalloc": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     },
     "attention_prefill": {
-        "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+        "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     },
     "attention_prefill_tc": {
         "ni_attention_prefill_tc": [_P, _P, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
@@ -1099,8 +1100,9 @@ def attention_decode_cluster_merge(on: bool) -> None:
 
 def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,
                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, scratch,
-                     tickets, warm=()) -> None:
-    """Split-K attention of single query tokens (bfloat16).  ``token_list`` int32 [n_items] or
+                     tickets, warm=(), score_cap: float = 0.0) -> None:
+    """Split-K attention of single query tokens (bfloat16).  ``score_cap`` c > 0 bounds the scaled scores:
+    s <- c * tanh(s / c).  ``token_list`` int32 [n_items] or
     None for tokens 0..n_items-1.  scratch: float32, at least n_items * Hq * n_splits *
     (head_dim + 2); tickets: int32 zeros, at least n_items * Hkv (left zero by the kernel).
     ``warm``: up to two (tensor, first byte, bytes) (weights that the kernels after it read): the
@@ -1110,13 +1112,15 @@ def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, s
         raise KernelError(f"attention_decode: head_dim {head_dim} / group {n_q_heads // n_kv_heads} not supported")
     if scratch.numel() < n_items * n_q_heads * n_splits * (head_dim + 2) or tickets.numel() < n_items * n_kv_heads:
         raise KernelError("attention_decode: scratch or tickets too small")
-    _check(load("attention_decode").ni_attention_decode(
+    lib = load("attention_decode")
+    capped = score_cap and score_cap > 0.0
+    _check((lib.ni_attention_decode_capped if capped else lib.ni_attention_decode)(
         _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
         _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),
         _dev(token_list, "token_list", torch.int32) if token_list is not None else None, n_items,
         _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
-        head_dim, page_size, int(window) if window else 0, float(scale), n_splits,
+        head_dim, page_size, int(window) if window else 0, float(scale), *((float(score_cap),) if capped else ()), n_splits,
         _dev(scratch, "scratch", torch.float32), _dev(tickets, "tickets", torch.int32),
         *regions, _stream()), "attention_decode")
 
@@ -1130,14 +1134,16 @@ def attention_prefill_tc_supports(n_q_heads: int, n_kv_heads: int, head_dim: int
 
 
 def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len, block_table,
-                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale, kernel: Optional[str] = None) -> None:
-    """Flash-style causal attention of prompt portions (bfloat16): one block per tile of
+                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale, kernel: Optional[str] = None,
+                      score_cap: float = 0.0) -> None:
+    """``score_cap`` c > 0 bounds the scaled scores, s <- c * tanh(s / c) (the mma.sync kernel only).
+    Flash-style causal attention of prompt portions (bfloat16): one block per tile of
     PREFILL_TILE_ROWS query rows and query head (mma.sync kernel) or pair of query heads
     (tcgen05 kernel, where it takes the case); tile_seq / tile_row0 int32 [n_tiles] name each
     tile's request and first row.  ``kernel``: "tc" or "mma" to insist on one of the two."""
     if head_dim % 16 or head_dim > PREFILL_MAX_HEAD_DIM:
         raise KernelError(f"attention_prefill: head_dim {head_dim} not supported (multiples of 16 up to 128)")
-    tc_ok = attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size)
+    tc_ok = attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size) and not score_cap
     if kernel == "tc" and not tc_ok:
         raise KernelError("attention_prefill: the tcgen05 kernel does not take this case")
     if tc_ok and kernel != "mma":
@@ -1156,7 +1162,8 @@ def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu
         _dev(tile_seq, "tile_seq", torch.int32), _dev(tile_row0, "tile_row0", torch.int32), n_tiles,
         _dev(cu_q, "cu_q", torch.int32), _dev(kv_len, "kv_len", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
-        head_dim, page_size, int(window) if window else 0, float(scale), _stream()), "attention_prefill")
+        head_dim, page_size, int(window) if window else 0, float(scale), float(score_cap or 0.0), _stream()),
+        "attention_prefill")
 
 
 _argmax_keys: Dict[torch.device, torch.Tensor] = {}   # per device: merge keys, zero between calls

@@ -127,7 +127,7 @@ def parse_config(raw: Dict[str, Any]) -> ModelConfig:
     return ModelConfig(
         architecture=NAME, hidden_size=width, vocab_size=vocab, max_position_embeddings=NO_POSITION_LIMIT,
         layers=tuple(layers), schedule=tuple(schedule), final_norm=norm, tie_word_embeddings=True,
-        embedding=EmbeddingSpec(kind="table", extra=(("scale", emb_scale),)),
+        embedding=EmbeddingSpec(kind="table", extra=(("row_scale", emb_scale),)),
         head=HeadSpec(kind="linear", tied=True, extra=(("logit_scale", logit_scale),)),
         stream_inputs=passes, raw=tuple(sorted((k, repr(v)) for k, v in raw.items())))
 

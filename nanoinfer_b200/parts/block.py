@@ -247,9 +247,15 @@ class SandwichNormBlock:
             delta = None                                   # the stream is up to date; this norm is computed here
         if delta is not None:
             ops.residual_add(h, delta)
-        self._sublayer(self.mixer, self.mixer_norm, self.mixer_post, h, (ctx, cache))
-        if self.feed_forward is not None:
-            self._sublayer(self.feed_forward, self.ffn_norm, self.ffn_post, h, (ctx,))
+        after = ctx.read_after                       # what runs after this block
+        ffn = self.feed_forward
+        ctx.read_after = (tuple(getattr(ffn, "weights_in_order", tuple)()) if ffn is not None else ()) + tuple(after)
+        try:
+            self._sublayer(self.mixer, self.mixer_norm, self.mixer_post, h, (ctx, cache))
+        finally:
+            ctx.read_after = after
+        if ffn is not None:
+            self._sublayer(ffn, self.ffn_norm, self.ffn_post, h, (ctx,))
         return None
 
 

@@ -15,7 +15,7 @@ class TableEmbedding(Part):
     precision, here it is FP32 from the first row on).
 
     ``table`` is the matrix on the device in the compute dtype; a tied head reads it too.
-    ``scale`` in the spec's extra (1 by default) multiplies every row as it enters the stream; the
+    ``row_scale`` in the spec's extra (1 by default) multiplies every row as it enters the stream; the
     table itself, which a tied head reads, stays as stored."""
 
     graph_safe = "all"
@@ -27,7 +27,7 @@ class TableEmbedding(Part):
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
         self.table = rt.weight(weights["weight"])
-        self.scale = float(spec.extra_dict().get("scale", 1.0))
+        self.scale = float(spec.extra_dict().get("row_scale", 1.0))
         if self.scale != 1.0:
             self.kernel_modules = ("pointwise",)      # the library of csrc that the scaled kernel lives in
 

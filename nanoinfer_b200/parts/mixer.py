@@ -60,9 +60,9 @@ class PagedAttendMixin:
         n = q.shape[0]
         slopes = getattr(self.position, "head_slopes", None)
         cap = float(getattr(self, "score_cap", 0.0))       # > 0: scores are bounded by cap * tanh(s / cap)
-        if rt.dtype != torch.bfloat16 or slopes is not None or cap > 0.0:
-            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)), or
-            # capped scores: the plain kernel takes all of them
+        if rt.dtype != torch.bfloat16 or slopes is not None:
+            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)):
+            # the plain kernel takes both; the tensor-core kernels know rotations and a cap on the scores
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                   table, *common, head_slopes=slopes, score_cap=cap)
             return
@@ -72,7 +72,8 @@ class PagedAttendMixin:
         n_dec = n if plan is None else plan.scalars["n_dec"]
         dec_list = None if plan is None else plan.arrays["dec_tokens"]
         if n_dec > 0:
-            if decode_ok and rt.balanced_attention(n_dec, self.n_kv, self.head_dim) and n_dec <= ops.DECODE_BALANCED_MAX_ITEMS:
+            if (decode_ok and cap == 0.0 and rt.balanced_attention(n_dec, self.n_kv, self.head_dim)
+                    and n_dec <= ops.DECODE_BALANCED_MAX_ITEMS):
                 # many tokens: their keys dealt evenly over a fixed set of blocks, whatever their lengths
                 scratch = rt.workspace("attention_decode_balanced_partials",
                                        ops.attention_decode_balanced_scratch(self.n_heads, self.n_kv, self.head_dim), torch.float32)
@@ -87,18 +88,18 @@ class PagedAttendMixin:
                 tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
                 ops.attention_decode(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
                                      ctx.seq_of_token, table, *common, splits, scratch, tickets,
-                                     warm=rt.warm_attention(self.w_o, ctx))
+                                     warm=rt.warm_attention(self.w_o, ctx), score_cap=cap)
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                      table, *common, token_list=dec_list)
+                                      table, *common, token_list=dec_list, score_cap=cap)
         if plan is not None and plan.scalars["n_tiles"] > 0:
             if prefill_ok:
                 ops.attention_prefill(q, cache.k_pages, cache.v_pages, att, plan.arrays["tile_seq"],
                                       plan.arrays["tile_row0"], plan.scalars["n_tiles"], ctx.cu_q, ctx.kv_len, table,
-                                      *common)
+                                      *common, score_cap=cap)
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                      table, *common, token_list=plan.arrays["long_tokens"])
+                                      table, *common, token_list=plan.arrays["long_tokens"], score_cap=cap)
 
 
 class PagedAttention(PagedAttendMixin, Part):

@@ -257,6 +257,62 @@ def test_attention_with_capped_scores(dtype, Hq, Hkv, D, cap):
         assert (want - free).abs().max() > 0.05
 
 
+@pytest.mark.parametrize("Hq, Hkv, D, cap", [(8, 2, 64, 3.0), (4, 1, 128, 1.5), (6, 3, 96, 4.0), (2, 2, 64, 2.0), (3, 1, 128, 6.0)])
+def test_tensor_core_attention_with_capped_scores(Hq, Hkv, D, cap):
+    """The bfloat16 kernels for prompt portions (mma.sync) and for single tokens (split over the keys) take the
+    cap too: portions of 300 and 150 tokens behind contexts of 0 and 77, and single tokens at contexts of 1 to
+    700, against the plain kernel (which the test above holds against the plain implementation)."""
+    from nanoinfer_b200.kernels import ops
+    from nanoinfer_b200.parts.mixer import PagedAttendMixin
+    g = torch.Generator().manual_seed(D * Hq)
+    bf, i32, page = torch.bfloat16, torch.int32, 16
+    n_pages = 100
+    k_pages = torch.randn(n_pages, Hkv, page, D, generator=g).to(bf).to(DEV)
+    k_pages[:, :, 3] *= 5.0                            # keys whose raw scores lie far beyond the cap
+    v_pages = torch.randn(n_pages, Hkv, page, D, generator=g).to(bf).to(DEV)
+    perm = torch.randperm(n_pages, generator=g).int()
+
+    def run(q_lens, starts):
+        n = sum(q_lens)
+        q = torch.randn(n, Hq * D, generator=g).to(bf).to(DEV)
+        kv = [a + b for a, b in zip(q_lens, starts)]
+        width = max(-(-x // page) for x in kv)
+        table = torch.zeros(len(q_lens), width, dtype=i32)
+        at = 0
+        for i, x in enumerate(kv):
+            need = -(-x // page)
+            table[i, :need] = perm[at:at + need]
+            at += need
+        pos = torch.cat([torch.arange(s, s + l) for s, l in zip(starts, q_lens)]).int().to(DEV)
+        seq = torch.repeat_interleave(torch.arange(len(q_lens)), torch.tensor(q_lens)).int().to(DEV)
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=i32, device=DEV)
+        table = table.to(DEV)
+        want = torch.empty_like(q)
+        ops.attention_generic(q, k_pages, v_pages, want, pos, seq, table, Hq, Hkv, D, page, None, 0.11, score_cap=cap)
+        free = torch.empty_like(q)
+        ops.attention_generic(q, k_pages, v_pages, free, pos, seq, table, Hq, Hkv, D, page, None, 0.11)
+        assert (want.float() - free.float()).abs().max() > 0.05, "the cap must bite"
+        got = torch.empty_like(q)
+        if max(q_lens) == 1:
+            if D not in ops.DECODE_HEAD_DIMS:
+                return
+            splits = ops.decode_splits(n, Hkv, D, max(kv))
+            scratch = torch.empty(n * Hq * splits * (D + 2), dtype=torch.float32, device=DEV)
+            tickets = torch.zeros(n * Hkv, dtype=i32, device=DEV)
+            ops.attention_decode(q, k_pages, v_pages, got, None, n, pos, seq, table, Hq, Hkv, D, page, None, 0.11, splits,
+                                 scratch, tickets, score_cap=cap)
+        else:
+            plan = PagedAttendMixin.plan_step(q_lens, starts)
+            ops.attention_prefill(q, k_pages, v_pages, got, torch.from_numpy(plan.arrays["tile_seq"]).to(DEV),
+                                  torch.from_numpy(plan.arrays["tile_row0"]).to(DEV), plan.scalars["n_tiles"], cu,
+                                  torch.tensor(kv, dtype=i32, device=DEV), table, Hq, Hkv, D, page, None, 0.11, kernel="mma",
+                                  score_cap=cap)
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+    run([300, 150], [0, 77])
+    run([1, 1, 1, 1], [0, 15, 256, 699])
+
+
 @pytest.mark.parametrize("n_real, n_id, top, d, f, n", [(5, 1, 2, 96, 40, 3), (5, 1, 2, 96, 40, 150), (8, 0, 3, 128, 64, 16),
                                                         (2, 3, 1, 64, 32, 70), (3, 1, 2, 76, 12, 40), (0, 2, 1, 64, 8, 9),
                                                         (40, 2, 6, 64, 16, 300)])

@@ -29,11 +29,11 @@ def test_config_becomes_parts_and_schedule():
     f = cfg.layers[3].feed_forward.extra_dict()
     assert (f["experts"], f["identity_experts"], f["top"], f["renormalize"]) == (6, 2, 3, False)
     assert cfg.layers[0].feed_forward.extra_dict()["limit"] == 0.8
-    assert cfg.embedding.extra_dict()["scale"] == 3.0 and cfg.head_spec().tied and cfg.head.extra_dict()["logit_scale"] == 0.7
+    assert cfg.embedding.extra_dict()["row_scale"] == 3.0 and cfg.head_spec().tied and cfg.head.extra_dict()["logit_scale"] == 0.7
     plain = config_from_dict(tv.V3)       # no loop, no scales, no rotation, no cap
     assert plain.stream_inputs == 0 and [r.layer for r in plain.schedule] == [0, 1]
     assert plain.layers[0].mixer.position.kind == "none" and plain.layers[0].mixer.extra_dict()["score_cap"] == 0.0
-    assert config_from_dict(tv.V2).embedding.extra_dict()["scale"] == 1.0
+    assert config_from_dict(tv.V2).embedding.extra_dict()["row_scale"] == 1.0
 
 
 def test_tensor_names_and_shapes():
