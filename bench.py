@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the Llama 3.2 1B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 16] [--impl ours|reference]
-    python bench.py --design runevik [--sizes w1024,w2048]     (another design beside the Llama model of equal size)
+    python bench.py --design runevik|vuvalorn [--sizes w1024,w2048]     (another design beside the Llama model of equal size)
 
 A "step" is one decode step of the whole batch.  Every request starts at a context of 2,048
 tokens and decodes W + K tokens (by default to 4,096).  Prints ONE JSON line:
@@ -399,6 +399,24 @@ def runevik_config(z):
             "token_side": {"dim": z["side"]}, "layers": layers}
 
 
+def vuvalorn_config(z):
+    """As many layer runs as the Llama model has layers: two layers fewer, a span of two that runs twice.  Layers
+    alternate between the capped unit and the routed one (16 experts and 2 identity experts, 4 chosen, each a
+    quarter of the dense width, so a token multiplies with as many feed-forward weights either way)."""
+    def layer(i):
+        mixer = {"heads": z["width"] // 128, "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "conv": 4,
+                 "rot": {"dims": 64, "base": 500000.0}, "scale": 128 ** -0.5, "softcap": 30.0}
+        mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "router": {"experts": 16, "identity": 2, "top": 4}}
+        return {"type": "attention", "mixer": mixer, "mlp": mlp}
+    return {"architecture": "Vuvalorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(z["width"]) ** 0.5}, "logit_scale": 1.0 / float(z["width"]) ** 0.5,
+            "loop": {"start": 2, "stop": 4, "times": 2}, "layers": [layer(i) for i in range(z["layers"] - 2)]}
+
+
+DESIGN_CONFIGS = {"runevik": runevik_config, "vuvalorn": vuvalorn_config}
+
+
 def llama_config(z):
     return {"architectures": ["LlamaForCausalLM"], "hidden_size": z["width"], "intermediate_size": z["ff"],
             "num_hidden_layers": z["layers"], "num_attention_heads": z["width"] // 128, "num_key_value_heads": z["kv_heads"],
@@ -407,7 +425,7 @@ def llama_config(z):
 
 
 def run_design(args):
-    """Prefill and decode throughput of the Runevik design beside the Llama model of equal size (random weights)."""
+    """Prefill and decode throughput of a design beside the Llama model of equal size (random weights)."""
     import torch
     from nanoinfer_b200.config import config_from_dict
     from nanoinfer_b200.engine import ModelRunner, StepEntry
@@ -425,7 +443,7 @@ def run_design(args):
     for size in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
         z = DESIGN_SIZES[size]
         row = {}
-        for name, raw in (("runevik", runevik_config(z)), ("llama", llama_config(z))):
+        for name, raw in ((args.design, DESIGN_CONFIGS[args.design](z)), ("llama", llama_config(z))):
             config = config_from_dict(raw)
             weights = device_weights(config, 0, device)
             per_request = -(-(max(ctx0 + W + K + 2, T)) // page)
@@ -471,7 +489,7 @@ def run_design(args):
            "dtype": "bf16", "data": "synthetic", "impl": "ours", "higher_is_better": True,
            "config": {"batch": B, "start_context": ctx0, "prefill_tokens": T, "kv_page_size": page,
                       "weights": "random N(0,0.02) bf16", "l2_policy": "inputs larger than L2 (weights and states per step)"},
-           "clocks": clocks.stop(), "designs": results}
+           "clocks": clocks.stop(), "design": args.design, "designs": results}
     print(json.dumps(out))
     return 0
 
@@ -488,7 +506,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode"] + sorted(WORKLOADS),
                     help="decode: the timed decode step (the published line); the others serve a set of requests")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")
-    ap.add_argument("--design", default=None, choices=["runevik"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGN_CONFIGS),
                     help="prefill and decode throughput of this design beside the Llama model of equal size, at a few sizes")
     ap.add_argument("--sizes", default=None, help="--design: which of " + ",".join(DESIGN_SIZES) + " (default: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

@@ -92,6 +92,128 @@ __global__ void conv_qk_prepare_kernel(const T* __restrict__ proj, int ld, const
     }
 }
 
+// The same with four neighbouring dimensions per lane (head sizes and row strides that are multiples of 4): the
+// projected values, the history and the results move in 8- or 16-byte pieces, and a rotated pair lies in one lane.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+        const uint2 x = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 x;
+        x.x = *reinterpret_cast<const uint32_t*>(&a);
+        x.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = x;
+    }
+};
+
+template <typename T, int CHUNKS>
+__global__ void conv_qk_prepare_vec_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+                                           const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                                           const float* __restrict__ state, long long state_stride,
+                                           const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                           const int* __restrict__ cu_q, const int* __restrict__ slots,
+                                           const int* __restrict__ block_table, int bt_stride,
+                                           const float* __restrict__ inv_freq, T* __restrict__ q_out,
+                                           T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int H, int G,
+                                           int D, int rot, int taps, int page_size) {
+    const int warps_per_block = blockDim.x >> 5;
+    const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * (H + G)) return;
+    const int lane = threadIdx.x & 31;
+    const int t = (int)(item / (H + G));
+    const int head = (int)(item - (long long)t * (H + G));
+    const bool is_key = head >= H;
+    const int C = (H + G) * D;
+    const int c0 = head * D;
+    const int seq = seq_of_token[t];
+    const int row0 = cu_q[seq];
+    const int local = t - row0;
+    const float* hist = state + (size_t)slots[seq] * state_stride;
+    const int pos = positions[t];
+
+    // What does not depend on the convolution is asked for first, so that its latency hides behind the
+    // convolution's loads: the gains, the page, the angles' sines and cosines.
+    const float* gain = is_key ? k_gain : q_gain;
+    int page = 0;
+    if (is_key && k_pages != nullptr) page = block_table[(size_t)seq * bt_stride + pos / page_size];
+    float gn[CHUNKS][4], sn[CHUNKS][2], cs[CHUNKS][2];
+#pragma unroll
+    for (int r = 0; r < CHUNKS; ++r) {
+        const int d0 = 4 * lane + 128 * r;
+        if (d0 < D) Vec4<float>::load(gain + d0, gn[r]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sn[r][i] = 0.f;
+            cs[r][i] = 1.f;
+            if (d0 + 2 * i < rot) sincosf(__fmul_rn((float)pos, inv_freq[(d0 + 2 * i) >> 1]), &sn[r][i], &cs[r][i]);
+        }
+    }
+
+    float y[CHUNKS][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < CHUNKS; ++r) {
+        const int d0 = 4 * lane + 128 * r;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[r][i] = 0.f;
+        if (d0 < D) {
+            const int c = c0 + d0;
+            const float* wc = conv_w + (size_t)c * taps;
+            for (int j = 0; j < taps; ++j) {
+                const int src = local - (taps - 1) + j;
+                float u[4];
+                if (src >= 0) Vec4<T>::load(proj + (size_t)(row0 + src) * ld + c, u);
+                else Vec4<float>::load(hist + (size_t)(taps - 1 + src) * C + c, u);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) y[r][i] = fmaf(wc[i * taps + j], u[i], y[r][i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ss += y[r][i] * y[r][i];
+        }
+    }
+    ss = ni_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+    T* dst;
+    T* vdst = nullptr;
+    if (is_key) {
+        if (k_pages == nullptr) return;
+        const size_t off = (((size_t)page * G + (head - H)) * page_size + (pos % page_size)) * D;
+        dst = k_pages + off;
+        vdst = v_pages + off;
+    } else {
+        dst = q_out + ((size_t)t * H + head) * D;
+    }
+#pragma unroll
+    for (int r = 0; r < CHUNKS; ++r) {
+        const int d0 = 4 * lane + 128 * r;
+        if (d0 >= D) continue;
+        float n[4], o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) n[i] = y[r][i] * inv * gn[r][i];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {             // a pair that is not rotated has sine 0 and cosine 1
+            o[2 * i] = fmaf(n[2 * i], cs[r][i], -n[2 * i + 1] * sn[r][i]);
+            o[2 * i + 1] = fmaf(n[2 * i + 1], cs[r][i], n[2 * i] * sn[r][i]);
+        }
+        Vec4<T>::store(dst + d0, o);
+        if (vdst != nullptr) Vec4<T>::store(vdst + d0, y[r]);
+    }
+}
+
 // state[slot][r, c] <- the projected value of channel c at the sequence's place (end - (taps - 1) + r): from the
 // portion where it reaches that far back, else from the old history, shifted (rows ascend, so a thread reads
 // a row before it overwrites it).
@@ -131,9 +253,18 @@ NI_EXPORT int ni_conv_qk_prepare(const void* proj, int dtype, int ld, const floa
         (const T*)proj, ld, conv_w, q_gain, k_gain, eps, state, state_stride, positions, seq_of_token, cu_q,    \
         slots, block_table, bt_stride, inv_freq, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, H, G, D, rot,   \
         taps, page_size)
+#define LAUNCH_V(T, R)                                                                                          \
+    conv_qk_prepare_vec_kernel<T, R><<<(int)blocks, warps * 32, 0, stream>>>(                                   \
+        (const T*)proj, ld, conv_w, q_gain, k_gain, eps, state, state_stride, positions, seq_of_token, cu_q,    \
+        slots, block_table, bt_stride, inv_freq, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, H, G, D, rot,   \
+        taps, page_size)
+    const bool vec = (D % 4 == 0) && (ld % 4 == 0);      // whole 8- or 16-byte pieces everywhere
 #define LAUNCH(T)                                          \
     do {                                                   \
-        if (D <= 128) LAUNCH_R(T, 4);                      \
+        if (vec && D <= 128) LAUNCH_V(T, 1);               \
+        else if (vec && D <= 256) LAUNCH_V(T, 2);          \
+        else if (vec) LAUNCH_V(T, 4);                      \
+        else if (D <= 128) LAUNCH_R(T, 4);                 \
         else if (D <= 256) LAUNCH_R(T, 8);                 \
         else LAUNCH_R(T, 16);                              \
     } while (0)
@@ -142,6 +273,7 @@ NI_EXPORT int ni_conv_qk_prepare(const void* proj, int dtype, int ld, const floa
     else return NI_ERR_BAD_ARGUMENT;
 #undef LAUNCH
 #undef LAUNCH_R
+#undef LAUNCH_V
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (taps > 1) {

@@ -3,13 +3,15 @@
 //   route     z = W_router x, s = softmax(z) over all experts, all FP32; the `top` experts with the largest
 //             s + bias are chosen (ties: the lower index), their weights are s (optionally divided by their sum).
 //             Experts numbered n_real and above are identity experts: their output is x itself.
-//   few rows  one warp per (token, choice, output): the expert's rows are streamed with 16-byte loads
-//             (expert_gate_up_rows: silu(gate) * up; expert_down_rows)
-//   many rows the (token, choice) pairs are laid out expert by expert (layout + scatter; where a pair lands
+//   layout    the (token, choice) pairs are laid out expert by expert (layout + scatter; where a pair lands
 //             inside its expert's stretch is decided by an atomic counter and changes no result, since every
-//             row is computed on its own), and one launch multiplies every stretch with its expert's matrix
-//             (expert_gemm: each output element is ONE chain of fused multiply-adds over k ascending, in
-//             FP32, whatever the row's place in a tile)
+//             row is computed on its own)
+//   few rows  bfloat16, fewer pairs than experts: one warp per (pair, output) streams the expert's row with 16-byte
+//             loads (expert_rows: silu(gate) * up, or the plain product); no layout is needed
+//             (with as many pairs as experts or more, the part multiplies with ALL experts' matrices in one
+//             skinny product instead, which reads every matrix once, and the combination picks the chosen rows)
+//   many rows one launch multiplies every stretch with its expert's matrix (expert_gemm: each output element is
+//             ONE chain of fused multiply-adds over k ascending, in FP32, whatever the row's place in a tile)
 //   combine   y[t] = sum over the token's choices, in the order they were chosen, of weight * (expert output
 //             or x[t]), FP32
 //
@@ -17,42 +19,60 @@
 #include "common.cuh"
 
 #define RT_MAX_EXPERTS 256
-#define RT_ROUTE_WARPS 4
+#define RT_ROUTE_WARPS 8
 
+// One block per token: the token's row is widened to FP32 in shared memory once, the warps share the experts'
+// dot products (each one warp's sum in a fixed order), and the first warp does the softmax and the choice.
 template <typename T>
-__global__ void route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
-                             const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
-                             int* __restrict__ counts, int n_tokens, int d, int n_all, int n_real, int top,
-                             int renormalize) {
-    __shared__ float choice[RT_ROUTE_WARPS][RT_MAX_EXPERTS];
-    __shared__ float score[RT_ROUTE_WARPS][RT_MAX_EXPERTS];
+__global__ void __launch_bounds__(RT_ROUTE_WARPS * 32)
+route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
+             const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
+             int* __restrict__ counts, int n_tokens, int d, int n_all, int n_real, int top,
+             int renormalize) {
+    extern __shared__ __align__(16) float xs[];          // [d]
+    __shared__ float choice[RT_MAX_EXPERTS];
+    __shared__ float score[RT_MAX_EXPERTS];
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * RT_ROUTE_WARPS + w;
-    if (t >= n_tokens) return;
+    const int t = blockIdx.x;
     const T* xr = x + (size_t)t * d;
-    for (int e = 0; e < n_all; ++e) {
+    for (int k = threadIdx.x; k < d; k += blockDim.x) xs[k] = ni_to_float(xr[k]);
+    __syncthreads();
+    for (int e = w; e < n_all; e += RT_ROUTE_WARPS) {
         const float* wr = w_router + (size_t)e * d;
         float acc = 0.f;
-        for (int k = lane; k < d; k += 32) acc = fmaf(ni_to_float(xr[k]), wr[k], acc);
+        if ((d & 3) == 0) {
+            const float4* w4 = reinterpret_cast<const float4*>(wr);
+            const float4* x4 = reinterpret_cast<const float4*>(xs);
+            for (int k = lane; k < (d >> 2); k += 32) {
+                const float4 a = x4[k], b = w4[k];
+                acc = fmaf(a.x, b.x, acc);
+                acc = fmaf(a.y, b.y, acc);
+                acc = fmaf(a.z, b.z, acc);
+                acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (int k = lane; k < d; k += 32) acc = fmaf(xs[k], wr[k], acc);
+        }
         acc = ni_warp_sum(acc);
-        if (lane == 0) score[w][e] = acc;
+        if (lane == 0) score[e] = acc;
     }
-    __syncwarp();
+    __syncthreads();
+    if (w != 0) return;
     float m = -INFINITY;
-    for (int e = lane; e < n_all; e += 32) m = fmaxf(m, score[w][e]);
+    for (int e = lane; e < n_all; e += 32) m = fmaxf(m, score[e]);
     m = ni_warp_max(m);
     float sum = 0.f;
     for (int e = lane; e < n_all; e += 32) {
-        const float p = expf(score[w][e] - m);
-        score[w][e] = p;
+        const float p = expf(score[e] - m);
+        score[e] = p;
         sum += p;
     }
     sum = ni_warp_sum(sum);
     const float inv = 1.0f / sum;
     for (int e = lane; e < n_all; e += 32) {
-        const float s = score[w][e] * inv;
-        score[w][e] = s;
-        choice[w][e] = s + (bias ? bias[e] : 0.f);
+        const float s = score[e] * inv;
+        score[e] = s;
+        choice[e] = s + (bias ? bias[e] : 0.f);
     }
     __syncwarp();
     float wsum = 0.f;
@@ -60,7 +80,7 @@ __global__ void route_kernel(const T* __restrict__ x, const float* __restrict__ 
         float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int e = lane; e < n_all; e += 32) {
-            const float c = choice[w][e];
+            const float c = choice[e];
             if (c > best) { best = c; arg = e; }       // ascending e: the first of equals stays
         }
 #pragma unroll
@@ -70,12 +90,12 @@ __global__ void route_kernel(const T* __restrict__ x, const float* __restrict__ 
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
         if (arg >= n_all) arg = j;                      // only if every remaining score is NaN: keep indices valid
-        const float s = score[w][arg];
+        const float s = score[arg];
         wsum += s;
         if (lane == 0) {
             ids[(size_t)t * top + j] = arg;
             weights[(size_t)t * top + j] = s;
-            choice[w][arg] = -INFINITY;
+            choice[arg] = -INFINITY;
             if (arg < n_real && counts) atomicAdd(&counts[arg], 1);
         }
         __syncwarp();
@@ -260,22 +280,52 @@ __global__ void expert_rows_kernel(const __nv_bfloat16* __restrict__ a, const __
 }
 
 // y[t, :] = sum_j weights[t, j] * (expert rows: z[row of pair (t, j), :];  identity experts: x[t, :]), FP32
+// all_experts > 0: z holds a row for every (token, expert), [T, all_experts, d], and pair p's row is t * all_experts + ids[p]
 template <typename T>
 __global__ void combine_kernel(const T* __restrict__ z, const T* __restrict__ x, const int* __restrict__ ids,
                                const float* __restrict__ weights, const int* __restrict__ row_of_pair,
-                               float* __restrict__ y, int d, int top, int n_real) {
+                               float* __restrict__ y, int d, int top, int n_real, int all_experts) {
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < top; ++j) {
             const int p = t * top + j;
             const float wgt = weights[p];
-            const float v = ids[p] >= n_real ? ni_to_float(x[(size_t)t * d + c])
-                                             : ni_to_float(z[(size_t)(row_of_pair ? row_of_pair[p] : p) * d + c]);
+            const int e = ids[p];
+            const int row = all_experts > 0 ? t * all_experts + e : (row_of_pair ? row_of_pair[p] : p);
+            const float v = e >= n_real ? ni_to_float(x[(size_t)t * d + c]) : ni_to_float(z[(size_t)row * d + c]);
             acc = fmaf(wgt, v, acc);
         }
         y[(size_t)t * d + c] = acc;
     }
+}
+
+// The same sum, divided by its root mean square, times a gain, added into the FP32 stream: h[t] += y / rms(y) * gain
+// (the norm that an arrangement puts on a sublayer's output, without a round trip of y through memory).
+template <typename T>
+__global__ void combine_add_normed_kernel(const T* __restrict__ z, const T* __restrict__ x, const int* __restrict__ ids,
+                                          const float* __restrict__ weights, const int* __restrict__ row_of_pair,
+                                          float* __restrict__ h, const float* __restrict__ gain, float eps, int d, int top,
+                                          int n_real, int all_experts) {
+    extern __shared__ float ys[];          // [d]
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int p = t * top + j;
+            const int e = ids[p];
+            const int row = all_experts > 0 ? t * all_experts + e : (row_of_pair ? row_of_pair[p] : p);
+            const float v = e >= n_real ? ni_to_float(x[(size_t)t * d + c]) : ni_to_float(z[(size_t)row * d + c]);
+            acc = fmaf(weights[p], v, acc);
+        }
+        ys[c] = acc;
+        ss += acc * acc;
+    }
+    ss = ni_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) h[(size_t)t * d + c] += ys[c] * inv * gain[c];
 }
 
 NI_EXPORT int ni_route(const void* x, int dtype, const float* w_router, const float* bias, int* ids, float* weights,
@@ -284,14 +334,15 @@ NI_EXPORT int ni_route(const void* x, int dtype, const float* w_router, const fl
     if (n_tokens <= 0) return NI_OK;
     if (d <= 0 || n_all <= 0 || n_real < 0 || n_real > n_all || top <= 0 || top > n_all) return NI_ERR_BAD_ARGUMENT;
     if (n_all > RT_MAX_EXPERTS || (renormalize && top > 32)) return NI_ERR_UNSUPPORTED_SIZE;
-    const int blocks = (n_tokens + RT_ROUTE_WARPS - 1) / RT_ROUTE_WARPS;
+    if (d > 12000) return NI_ERR_UNSUPPORTED_SIZE;                    // the row lies in shared memory as FP32
+    const size_t smem = (size_t)d * sizeof(float);
     if (dtype == NI_DTYPE_F32)
-        route_kernel<float><<<blocks, RT_ROUTE_WARPS * 32, 0, stream>>>((const float*)x, w_router, bias, ids, weights, counts,
-                                                                      n_tokens, d, n_all, n_real, top, renormalize);
+        route_kernel<float><<<n_tokens, RT_ROUTE_WARPS * 32, smem, stream>>>((const float*)x, w_router, bias, ids, weights,
+                                                                           counts, n_tokens, d, n_all, n_real, top, renormalize);
     else if (dtype == NI_DTYPE_BF16)
-        route_kernel<__nv_bfloat16><<<blocks, RT_ROUTE_WARPS * 32, 0, stream>>>((const __nv_bfloat16*)x, w_router, bias, ids,
-                                                                              weights, counts, n_tokens, d, n_all, n_real,
-                                                                              top, renormalize);
+        route_kernel<__nv_bfloat16><<<n_tokens, RT_ROUTE_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)x, w_router, bias,
+                                                                                   ids, weights, counts, n_tokens, d, n_all,
+                                                                                   n_real, top, renormalize);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();
@@ -343,18 +394,37 @@ NI_EXPORT int ni_expert_rows(const void* a, const void* w, void* out, const int*
     NI_RETURN_LAUNCH_STATUS();
 }
 
+NI_EXPORT int ni_route_combine_add_normed(const void* z, const void* x, int dtype, const int* ids, const float* weights,
+                                          const int* row_of_pair, float* h, const float* gain, float eps, int n_tokens,
+                                          int d, int top, int n_real, int all_experts, cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (d <= 0 || top <= 0) return NI_ERR_BAD_ARGUMENT;
+    if (d > 12000) return NI_ERR_UNSUPPORTED_SIZE;
+    const int threads = d >= 1024 ? 256 : 128;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (dtype == NI_DTYPE_F32)
+        combine_add_normed_kernel<float><<<n_tokens, threads, smem, stream>>>((const float*)z, (const float*)x, ids, weights,
+                                                                             row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+    else if (dtype == NI_DTYPE_BF16)
+        combine_add_normed_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
+            (const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
+}
+
 NI_EXPORT int ni_route_combine(const void* z, const void* x, int dtype, const int* ids, const float* weights,
                                const int* row_of_pair, float* y, int n_tokens, int d, int top, int n_real,
-                               cudaStream_t stream) {
+                               int all_experts, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (d <= 0 || top <= 0) return NI_ERR_BAD_ARGUMENT;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == NI_DTYPE_F32)
         combine_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)z, (const float*)x, ids, weights, row_of_pair, y,
-                                                               d, top, n_real);
+                                                               d, top, n_real, all_experts);
     else if (dtype == NI_DTYPE_BF16)
         combine_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids,
-                                                                       weights, row_of_pair, y, d, top, n_real);
+                                                                       weights, row_of_pair, y, d, top, n_real, all_experts);
     else
         return NI_ERR_BAD_ARGUMENT;
     NI_RETURN_LAUNCH_STATUS();

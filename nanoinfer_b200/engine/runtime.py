@@ -170,6 +170,29 @@ class Runtime:
             torch.bmm(x.view(t, n_heads, k).transpose(0, 1), w.transpose(1, 2), out=y.view(t, n_heads, n).transpose(0, 1))
         return y
 
+    def experts_linear(self, a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, tile_first: torch.Tensor,
+                       n_rows: int, token_of_row: Optional[torch.Tensor] = None, act: bool = False) -> torch.Tensor:
+        """One product per expert over rows laid out expert by expert: y[r] = a[r] . w[e]^T for the rows r of
+        expert e's stretch [offsets[e], offsets[e + 1]) (int32 on the device; nothing is read on the host).
+        ``token_of_row``: row r reads a[token_of_row[r]] instead.  ``act``: w is [E, 2N, K], gate rows then up
+        rows, and y = silu(gate) * up.  float32: the package's FFMA kernel, one ascending chain per element;
+        bfloat16 with sizes that are multiples of 8: a library grouped product (FP32 accumulation), as the
+        other projections of prompt portions are library products; rows beyond the last stretch are undefined."""
+        n_experts, wn, k = w.shape
+        n = wn // 2 if act else wn
+        if self.dtype == torch.bfloat16 and k % 8 == 0 and wn % 8 == 0 and n % 8 == 0:
+            if token_of_row is not None:
+                a = torch.index_select(a, 0, token_of_row[:n_rows])
+            y = torch.nn.functional.grouped_mm(a[:n_rows], w.transpose(1, 2), offs=offsets[1:n_experts + 1])
+            if not act:
+                return y
+            out = self.empty(n_rows, n)
+            ops.capped_glu(y, out, float("inf"), 1.0, 0.0)      # no cap, slope 1, no shift: silu(gate) * up, 16 bytes per thread
+            return out
+        out = self.empty(n_rows, n)
+        ops.expert_gemm(a, token_of_row, w, out, offsets, tile_first, n_rows, act=act)
+        return out
+
     def skinny(self, n_rows: int, k: int) -> bool:
         """True if a product of n_rows activations with inner size k goes to the package's own
         bandwidth kernel (and so may carry fused prologues and epilogues)."""

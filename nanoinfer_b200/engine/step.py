@@ -200,20 +200,24 @@ class ModelRunner:
         self.config = config
         self.rt = Runtime(device=torch.device(device), dtype=parse_dtype(dtype), page_size=page_size,
                           fused_decode=fused_decode)
-        # compile (in parallel) and load what this precision needs before the first step
         from ..kernels import ops
-        common = ["elementwise", "rope_kv", "attention_generic"]
-        ops.preload(common + (["gemm_f32"] if self.rt.dtype == torch.float32 else
-                              ["gemv_bf16", "gemv_ksplit", "gemm_tc", "gemm_tc2", "gemm_swap_tc", "attention_prefill", "attention_prefill_tc", "attention_decode"]
-                              + (["decode_fused"] if fused_decode else [])))
         self.model = DecoderModel(config, weights, self.rt)
-        # libraries that only some parts use (a part names them in ``kernel_modules``): built together, now
-        extra = sorted({m for b in self.model.blocks for p in (b, getattr(b, "mixer", None), getattr(b, "feed_forward", None))
-                        for m in getattr(p, "kernel_modules", ())}
-                       | set(getattr(self.model.embedding, "kernel_modules", ()))
-                       | set(getattr(self.model.head, "kernel_modules", ())))
-        if extra:
-            ops.preload(extra)
+        # Compile (in parallel) and load what THIS model needs in this precision before the first step: the
+        # libraries every model uses, and those its parts name (``kernel_modules``, and ``kernel_modules_bf16``
+        # for the bfloat16 path only; a class inherits its bases' lists).  Anything else is built when first used.
+        bf16 = self.rt.dtype == torch.bfloat16
+        needed = {"elementwise"} | ({"gemv_bf16", "gemv_ksplit"} if bf16 else {"gemm_f32"}) | ({"decode_fused"} if fused_decode else set())
+        all_parts = [p for b in self.model.blocks for p in (b, getattr(b, "mixer", None), getattr(b, "feed_forward", None))] \
+            + [self.model.embedding, self.model.head]
+        for part in all_parts:
+            if part is None:
+                continue
+            needed |= set(getattr(part, "__dict__", {}).get("kernel_modules", ()))            # set on the instance
+            for cls in type(part).__mro__:
+                needed |= set(cls.__dict__.get("kernel_modules", ()))
+                if bf16:
+                    needed |= set(cls.__dict__.get("kernel_modules_bf16", ()))
+        ops.preload(sorted(needed))
 
         # cache groups: one per distinct need among the runs that own a cache
         needs = self.model.cache_needs()

@@ -60,7 +60,8 @@ _SIGNATURES = {
         "ni_route_layout": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
         "ni_expert_gemm": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ni_expert_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-        "ni_route_combine": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "ni_route_combine": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ni_route_combine_add_normed": [_P, _P, _I, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _P],
     },
     "delta_rule": {
         "ni_delta_prepare": [_P, _P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
@@ -629,9 +630,10 @@ def expert_rows(a, w, out, ids, gather: bool, act: bool) -> None:
                                          n_pairs, top, 1 if gather else 0, e, n, k, 1 if act else 0, _stream()), "expert_rows")
 
 
-def route_combine(z, x, ids, weights, row_of_pair, y, n_real) -> None:
+def route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts: int = 0) -> None:
     """y[t] = sum_j weights[t, j] * (z[row of pair (t, j)] for a real expert, x[t] for an identity expert), in the
-    order of the choices, float32; row_of_pair None: pair p's row is p."""
+    order of the choices, float32; row_of_pair None: pair p's row is p; ``all_experts`` = E > 0: z holds a row
+    for every (token, expert), [T E, d], and the pair's row is t E + its expert."""
     n, top = ids.shape
     d = x.shape[1]
     if y.shape != (n, d) or z.shape[1] != d or z.dtype != x.dtype:
@@ -639,7 +641,21 @@ def route_combine(z, x, ids, weights, row_of_pair, y, n_real) -> None:
     _check(load("routed").ni_route_combine(_dev(z, "z"), _dev(x, "x"), _code(x, "x"), _dev(ids, "ids", torch.int32),
                                            _dev(weights, "weights", torch.float32),
                                            _dev(row_of_pair, "row_of_pair", torch.int32) if row_of_pair is not None else None,
-                                           _dev(y, "y", torch.float32), n, d, top, n_real, _stream()), "route_combine")
+                                           _dev(y, "y", torch.float32), n, d, top, n_real, int(all_experts), _stream()),
+           "route_combine")
+
+
+def route_combine_add_normed(z, x, ids, weights, row_of_pair, h, gain, eps, n_real, all_experts: int = 0) -> None:
+    """h[t] += y / sqrt(mean(y^2) + eps) * gain with y the sum that route_combine computes; h float32 [T, d]."""
+    n, top = ids.shape
+    d = x.shape[1]
+    if h.shape != (n, d) or z.shape[1] != d or z.dtype != x.dtype or gain.numel() != d:
+        raise KernelError("route_combine_add_normed: shapes or dtypes do not agree")
+    _check(load("routed").ni_route_combine_add_normed(
+        _dev(z, "z"), _dev(x, "x"), _code(x, "x"), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
+        _dev(row_of_pair, "row_of_pair", torch.int32) if row_of_pair is not None else None, _dev(h, "h", torch.float32),
+        _dev(gain, "gain", torch.float32), float(eps), n, d, top, n_real, int(all_experts), _stream()),
+        "route_combine_add_normed")
 
 
 GEMV_MAX_ROWS = 16      # what the skinny kernels take

@@ -236,11 +236,16 @@ class SandwichNormBlock:
 
     def _sublayer(self, sub, norm, post, h, args) -> None:
         rt = self.rt
+        into = {"normed_into": (h, post.gain, post.eps)} if getattr(sub, "adds_normed", False) else {}
         if (rt.skinny(h.shape[0], self.hidden_size) and rt.fuses_norm(norm) and hasattr(sub, "project")):
-            y = sub.finish(sub.project(h, norm), *args)      # a few rows: the norm runs inside the first product
+            y = sub.finish(sub.project(h, norm), *args, **into)      # a few rows: the norm runs inside the first product
+        elif into:
+            # a sublayer whose last kernel can norm its own output and add it into the stream
+            y = sub.forward(norm.forward(h, None), *args, normed_into=(h, post.gain, post.eps))
         else:
             y = sub.forward(norm.forward(h, None), *args)
-        ops.add_normed(h, y, post.gain, post.eps)
+        if y is not None:
+            ops.add_normed(h, y, post.gain, post.eps)
 
     def forward(self, h: torch.Tensor, delta, ctx, cache):
         if isinstance(delta, NormHandoff):

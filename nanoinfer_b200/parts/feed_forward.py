@@ -15,6 +15,8 @@ class SwiGLU(Part):
     """y = down(silu(gate(x)) * up(x)); gate and up are one fused projection
     (src/model/llama.cpp:364-379, src/op/kernels/cuda/swiglu_kernel.cu:25-40)."""
 
+    kernel_modules_bf16 = ("gemm_tc", "gemm_tc2", "gemm_swap_tc")      # libraries of csrc: the tcgen05 products with the activation inside
+
     @staticmethod
     def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
         i = spec.intermediate_size
@@ -184,12 +186,15 @@ class RoutedExperts(Part):
     chosen ones are those with the largest s + correction (``choice_bias``), their weights are s, divided by
     their sum only if ``renormalize``; the output is the weighted sum, FP32.
 
-    The experts' matrices are stacked ([E, 2F, d] gate rows then up rows, and [E, d, F]).  Steps of a few
-    (token, choice) pairs in bfloat16 stream each pair's expert with one warp per output; otherwise the pairs
+    The experts' matrices are stacked ([E, 2F, d] gate rows then up rows, and [E, d, F]).  In bfloat16, steps of a
+    few tokens with at least as many (token, choice) pairs as experts multiply with ALL experts' matrices (one
+    skinny product, each matrix read once, the norm before it inside) and pick the chosen rows afterwards; steps
+    with fewer pairs stream each pair's expert with one warp per output; otherwise the pairs
     are laid out expert by expert on the device and one launch per product multiplies every stretch with its
-    expert's matrix (csrc/routed.cu).  Nothing is decided on the host, so a step can be captured."""
+    expert's matrix (csrc/routed.cu in FP32; a library grouped product in bfloat16, see Runtime.experts_linear).
+    Nothing is decided on the host, so a step can be captured."""
 
-    kernel_modules = ("routed",)       # libraries of csrc that this part's kernels live in
+    kernel_modules = ("routed", "pointwise")       # libraries of csrc that this part's kernels live in
 
     adds_into_residual = False
     graph_safe = "all"
@@ -231,7 +236,48 @@ class RoutedExperts(Part):
     def weights_in_order(self) -> tuple:
         return (self.w_gate_up, self.w_down) if self.n_real > 0 else ()
 
-    def forward(self, x: torch.Tensor, ctx):
+    adds_normed = True          # forward accepts normed_into=(h, gain, eps): h += RMSNorm(output) * gain, returns None
+
+    def _combine(self, z, x, ids, weights, row_of_pair, n_real, normed_into, all_experts=0):
+        if normed_into is not None and x.shape[1] <= 12000:
+            h, gain, eps = normed_into
+            ops.route_combine_add_normed(z, x, ids, weights, row_of_pair, h, gain, eps, n_real, all_experts)
+            return None
+        y = self.rt.empty(x.shape[0], x.shape[1], dtype=torch.float32)
+        ops.route_combine(z, x, ids, weights, row_of_pair, y, n_real, all_experts)
+        if normed_into is not None:
+            ops.add_normed(normed_into[0], y, normed_into[1], normed_into[2])
+            return None
+        return y
+
+    def forward(self, x: torch.Tensor, ctx, normed_into=None):
+        return self.finish(self._first(x, None, None), ctx, normed_into=normed_into)
+
+    def project(self, h: torch.Tensor, norm):
+        """A few rows (bfloat16): the norm of the stream, and - where the step has at least as many (token, choice)
+        pairs as there are experts - the gate and up products of ALL experts, in one skinny product with the norm
+        inside it."""
+        return self._first(None, h, norm)
+
+    def _first(self, x, h, norm):
+        rt = self.rt
+        n = (x if x is not None else h).shape[0]
+        dense = (rt.dtype == torch.bfloat16 and self.n_real > 0 and rt.skinny(n, self.hidden_size)
+                 and n * self.top >= self.n_real and self.inter % 8 == 0)
+        if x is None:
+            x = norm.forward(h, None)                 # the router and the identity experts read the normed rows
+        gate_up_all = None
+        if dense:
+            w_all = self.w_gate_up.view(self.n_real * 2 * self.inter, self.hidden_size)
+            gate_up_all = rt.empty(n, w_all.shape[0])
+            if h is not None:
+                ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, w_all, gate_up_all, ops.STORE_BF16)
+            else:
+                ops.gemv_bf16(x, w_all, gate_up_all, ops.STORE_BF16)
+        return x, gate_up_all
+
+    def finish(self, first, ctx, normed_into=None):
+        x, gate_up_all = first
         rt = self.rt
         n, d = x.shape
         top, n_real, f = self.top, self.n_real, self.inter
@@ -239,33 +285,34 @@ class RoutedExperts(Part):
         i32 = torch.int32
         ids = rt.empty(n, top, dtype=i32)
         weights = rt.empty(n, top, dtype=torch.float32)
-        y = rt.empty(n, d, dtype=torch.float32)
-        few = (rt.dtype == torch.bfloat16 and pairs <= ops.EXPERT_ROWS_MAX_PAIRS and d % 8 == 0 and f % 8 == 0)
         if n_real == 0:
             ops.route(x, self.w_router, self.bias, ids, weights, None, 0, top, self.renormalize)
-            ops.route_combine(x, x, ids, weights, None, y, 0)
-            return y
+            return self._combine(x, x, ids, weights, None, 0, normed_into)
+        if gate_up_all is not None:
+            # every expert for every token: each matrix is read once, whoever chose it; the combination picks
+            ops.route(x, self.w_router, self.bias, ids, weights, None, n_real, top, self.renormalize)
+            act = rt.empty(n * n_real, f)
+            ops.capped_glu(gate_up_all.view(n * n_real, 2 * f), act, float("inf"), 1.0, 0.0)     # silu(gate) * up
+            z = rt.heads_linear(act.view(n, n_real * f), self.w_down)                           # [T, E d]
+            return self._combine(z.view(n * n_real, d), x, ids, weights, None, n_real, normed_into, all_experts=n_real)
+        few = (rt.dtype == torch.bfloat16 and pairs <= ops.EXPERT_ROWS_MAX_PAIRS and d % 8 == 0 and f % 8 == 0)
         if few:
             ops.route(x, self.w_router, self.bias, ids, weights, None, n_real, top, self.renormalize)
             act = rt.empty(pairs, f)
             ops.expert_rows(x, self.w_gate_up, act, ids, gather=True, act=True)
             z = rt.empty(pairs, d)
             ops.expert_rows(act, self.w_down, z, ids, gather=False, act=False)
-            ops.route_combine(z, x, ids, weights, None, y, n_real)
-            return y
+            return self._combine(z, x, ids, weights, None, n_real, normed_into)
         counts = rt.workspace("routed_counts", ops.ROUTE_MAX_EXPERTS, i32, zero=True)
         ops.route(x, self.w_router, self.bias, ids, weights, counts, n_real, top, self.renormalize)
-        meta = rt.empty(3 * (n_real + 1) + 2 * pairs, dtype=i32)
+        meta = torch.zeros(3 * (n_real + 1) + 2 * pairs, dtype=i32, device=rt.device)     # rows nobody owns name token 0
         offsets, tile_first, cursor = (meta[i * (n_real + 1):(i + 1) * (n_real + 1)] for i in range(3))
         row_of_pair = meta[3 * (n_real + 1):3 * (n_real + 1) + pairs]
         token_of_row = meta[3 * (n_real + 1) + pairs:]
         ops.route_layout(ids, counts, offsets, tile_first, cursor, row_of_pair, token_of_row, n_real)
-        act = rt.empty(pairs, f)
-        ops.expert_gemm(x, token_of_row, self.w_gate_up, act, offsets, tile_first, pairs, act=True)
-        z = rt.empty(pairs, d)
-        ops.expert_gemm(act, None, self.w_down, z, offsets, tile_first, pairs, act=False)
-        ops.route_combine(z, x, ids, weights, row_of_pair, y, n_real)
-        return y
+        act = rt.experts_linear(x, self.w_gate_up, offsets, tile_first, pairs, token_of_row=token_of_row, act=True)
+        z = rt.experts_linear(act, self.w_down, offsets, tile_first, pairs)
+        return self._combine(z, x, ids, weights, row_of_pair, n_real, normed_into)
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -24,6 +24,10 @@ class PagedAttendMixin:
     SHORT_PORTION = ops.DECODE_FRESH_KEYS
     TILE_ROWS = ops.PREFILL_TILE_ROWS
 
+    # libraries of csrc that the attention kernels live in (the second list: on the bfloat16 path only)
+    kernel_modules = ("attention_generic",)
+    kernel_modules_bf16 = ("attention_prefill", "attention_decode")
+
     @staticmethod
     def plan_step(q_lens: List[int], starts: List[int]) -> StepPlan:
         """dec_tokens: token indices of the short portions; long_tokens: of the long ones;
@@ -117,6 +121,9 @@ class PagedAttention(PagedAttendMixin, Part):
         q, kv = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
         return {"q": WeightSlot((q, hidden_size)), "k": WeightSlot((kv, hidden_size)),
                 "v": WeightSlot((kv, hidden_size)), "o": WeightSlot((hidden_size, q))}
+
+    kernel_modules = ("rope_kv",)
+    kernel_modules_bf16 = ("attention_prefill_tc", "gemm_swap_tc")     # prompt portions on tcgen05; middle batches
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
@@ -230,6 +237,7 @@ class LatentAttention(PagedAttendMixin, Part):
     and the result leaves through W_uv.  Projections of x (q | gate | dkv) are one product."""
 
     kernel_modules = ("latent",)       # libraries of csrc that this part's kernels live in
+    kernel_modules_bf16 = ("attention_prefill_tc",)
 
     @staticmethod
     def _dims(spec):
@@ -358,7 +366,11 @@ class ConvKeyAttention(PagedAttendMixin, Part):
         if getattr(self.position, "head_slopes", None) is not None:
             raise ConfigError("conv-key attention takes no position encoding that acts on the scores")
         self.channels = (h + g) * d
-        self.w_in = rt.weight(torch.cat([weights["q"], weights["k"], weights["g"]], dim=0))      # q | k | gate
+        rows = [weights["q"], weights["k"], weights["g"]]                                       # q | k | gate
+        pad = -(self.channels + h) % 8            # zero rows, so that every row of the result starts on 16 bytes
+        if pad:
+            rows.append(torch.zeros(pad, hidden_size, dtype=weights["q"].dtype, device=weights["q"].device))
+        self.w_in = rt.weight(torch.cat(rows, dim=0))
         self.w_o = rt.weight(weights["o"])
         self.conv_w = rt.gain(torch.cat([weights["q.conv"], weights["k.conv"]], dim=0))
         self.q_gain, self.k_gain = rt.gain(weights["q.norm"]), rt.gain(weights["k.norm"])

@@ -315,7 +315,8 @@ def test_tensor_core_attention_with_capped_scores(Hq, Hkv, D, cap):
 
 @pytest.mark.parametrize("n_real, n_id, top, d, f, n", [(5, 1, 2, 96, 40, 3), (5, 1, 2, 96, 40, 150), (8, 0, 3, 128, 64, 16),
                                                         (2, 3, 1, 64, 32, 70), (3, 1, 2, 76, 12, 40), (0, 2, 1, 64, 8, 9),
-                                                        (40, 2, 6, 64, 16, 300)])
+                                                        (40, 2, 6, 64, 16, 300), (8, 0, 3, 128, 64, 200), (6, 0, 6, 64, 24, 33), (8, 0, 3, 128, 64, 1),
+                                                        (16, 2, 4, 256, 64, 8)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_router_and_experts(dtype, n_real, n_id, top, d, f, n):
     """The routed part alone: choices and weights against the plain router, the output against the plain unit,
@@ -364,7 +365,8 @@ def test_router_and_experts(dtype, n_real, n_id, top, d, f, n):
     for t in range(n):
         if not close[t]:
             want = routed_unit(x[t].double(), w["router"].double(), w["correction"].double(), experts, top)
-            torch.testing.assert_close(y[t].double().cpu(), want, **tol)
+            scale = max(1.0, want.abs().max().item())             # bfloat16 roundings grow with the size of the sums
+            torch.testing.assert_close(y[t].double().cpu() / scale, want / scale, **tol)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
