@@ -3,7 +3,8 @@
 // into the paged cache, in one launch; and the request's convolution history.
 //
 //   u_t[c]  = the projected value of channel c at token t (q channels of all heads, then k channels)
-//   y_t[c]  = sum_j w[c, j] * u_(t - taps + 1 + j)[c]          (zeros before the sequence's start)
+//   y_t[c]  = sum_j w[j, c] * u_(t - taps + 1 + j)[c]          (zeros before the sequence's start; the taps are
+//             handed over tap-major, [taps, C], so that neighbouring lanes read neighbouring weights)
 //   value   = y of a key head, as it is                        -> value pages
 //   n       = y / sqrt(mean_head(y^2) + eps) * gain[d]         (gain shared by the heads; one for q, one for k)
 //   (a, b)  = (n[2i], n[2i+1]) -> (a cos - b sin, b cos + a sin), angle = position * inv_freq[i], i < rot / 2
@@ -52,7 +53,7 @@ __global__ void conv_qk_prepare_kernel(const T* __restrict__ proj, int ld, const
                 const int src = local - (taps - 1) + j;       // index inside the portion; negative: history
                 const float u = src >= 0 ? ni_to_float(proj[(size_t)(row0 + src) * ld + c])
                                          : hist[(size_t)(taps - 1 + src) * C + c];
-                acc = fmaf(conv_w[(size_t)c * taps + j], u, acc);
+                acc = fmaf(conv_w[(size_t)j * C + c], u, acc);
             }
             ss += acc * acc;
         }
@@ -120,97 +121,89 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
+// One block per token: the sines and cosines of the token's angles are computed once into shared memory and serve
+// all heads; the block's warps share the heads.
 template <typename T, int CHUNKS>
-__global__ void conv_qk_prepare_vec_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
-                                           const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
-                                           const float* __restrict__ state, long long state_stride,
-                                           const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                           const int* __restrict__ cu_q, const int* __restrict__ slots,
-                                           const int* __restrict__ block_table, int bt_stride,
-                                           const float* __restrict__ inv_freq, T* __restrict__ q_out,
-                                           T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int H, int G,
-                                           int D, int rot, int taps, int page_size) {
-    const int warps_per_block = blockDim.x >> 5;
-    const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-    if (item >= (long long)n_tokens * (H + G)) return;
-    const int lane = threadIdx.x & 31;
-    const int t = (int)(item / (H + G));
-    const int head = (int)(item - (long long)t * (H + G));
-    const bool is_key = head >= H;
-    const int C = (H + G) * D;
-    const int c0 = head * D;
+__global__ void __launch_bounds__(256)
+conv_qk_prepare_vec_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+                           const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                           const float* __restrict__ state, long long state_stride,
+                           const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                           const int* __restrict__ cu_q, const int* __restrict__ slots,
+                           const int* __restrict__ block_table, int bt_stride,
+                           const float* __restrict__ inv_freq, T* __restrict__ q_out,
+                           T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int H, int G,
+                           int D, int rot, int taps, int page_size) {
+    __shared__ float s_sin[256], s_cos[256];          // rot / 2 <= 256
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int pos = positions[t];
     const int seq = seq_of_token[t];
+    for (int i = threadIdx.x; i < (rot >> 1); i += blockDim.x) sincosf(__fmul_rn((float)pos, inv_freq[i]), &s_sin[i], &s_cos[i]);
+    const int C = (H + G) * D;
     const int row0 = cu_q[seq];
     const int local = t - row0;
     const float* hist = state + (size_t)slots[seq] * state_stride;
-    const int pos = positions[t];
-
-    // What does not depend on the convolution is asked for first, so that its latency hides behind the
-    // convolution's loads: the gains, the page, the angles' sines and cosines.
-    const float* gain = is_key ? k_gain : q_gain;
     int page = 0;
-    if (is_key && k_pages != nullptr) page = block_table[(size_t)seq * bt_stride + pos / page_size];
-    float gn[CHUNKS][4], sn[CHUNKS][2], cs[CHUNKS][2];
+    if (k_pages != nullptr) page = block_table[(size_t)seq * bt_stride + pos / page_size];
+    __syncthreads();
+    for (int head = warp + blockIdx.y * n_warps; head < H + G; head += n_warps * gridDim.y) {     // few tokens: the heads are dealt over several blocks
+        const bool is_key = head >= H;
+        if (is_key && k_pages == nullptr) continue;
+        const int c0 = head * D;
+        const float* gain = is_key ? k_gain : q_gain;
+        float y[CHUNKS][4];
+        float ss = 0.f;
 #pragma unroll
-    for (int r = 0; r < CHUNKS; ++r) {
-        const int d0 = 4 * lane + 128 * r;
-        if (d0 < D) Vec4<float>::load(gain + d0, gn[r]);
+        for (int r = 0; r < CHUNKS; ++r) {
+            const int d0 = 4 * lane + 128 * r;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            sn[r][i] = 0.f;
-            cs[r][i] = 1.f;
-            if (d0 + 2 * i < rot) sincosf(__fmul_rn((float)pos, inv_freq[(d0 + 2 * i) >> 1]), &sn[r][i], &cs[r][i]);
-        }
-    }
-
-    float y[CHUNKS][4];
-    float ss = 0.f;
+            for (int i = 0; i < 4; ++i) y[r][i] = 0.f;
+            if (d0 < D) {
+                const int c = c0 + d0;
+                for (int j = 0; j < taps; ++j) {
+                    const int src = local - (taps - 1) + j;
+                    float u[4], wj[4];
+                    Vec4<float>::load(conv_w + (size_t)j * C + c, wj);       // tap j of four neighbouring channels
+                    if (src >= 0) Vec4<T>::load(proj + (size_t)(row0 + src) * ld + c, u);
+                    else Vec4<float>::load(hist + (size_t)(taps - 1 + src) * C + c, u);
 #pragma unroll
-    for (int r = 0; r < CHUNKS; ++r) {
-        const int d0 = 4 * lane + 128 * r;
+                    for (int i = 0; i < 4; ++i) y[r][i] = fmaf(wj[i], u[i], y[r][i]);
+                }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) y[r][i] = 0.f;
-        if (d0 < D) {
-            const int c = c0 + d0;
-            const float* wc = conv_w + (size_t)c * taps;
-            for (int j = 0; j < taps; ++j) {
-                const int src = local - (taps - 1) + j;
-                float u[4];
-                if (src >= 0) Vec4<T>::load(proj + (size_t)(row0 + src) * ld + c, u);
-                else Vec4<float>::load(hist + (size_t)(taps - 1 + src) * C + c, u);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) y[r][i] = fmaf(wc[i * taps + j], u[i], y[r][i]);
+                for (int i = 0; i < 4; ++i) ss += y[r][i] * y[r][i];
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) ss += y[r][i] * y[r][i];
         }
-    }
-    ss = ni_warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-    T* dst;
-    T* vdst = nullptr;
-    if (is_key) {
-        if (k_pages == nullptr) return;
-        const size_t off = (((size_t)page * G + (head - H)) * page_size + (pos % page_size)) * D;
-        dst = k_pages + off;
-        vdst = v_pages + off;
-    } else {
-        dst = q_out + ((size_t)t * H + head) * D;
-    }
-#pragma unroll
-    for (int r = 0; r < CHUNKS; ++r) {
-        const int d0 = 4 * lane + 128 * r;
-        if (d0 >= D) continue;
-        float n[4], o[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) n[i] = y[r][i] * inv * gn[r][i];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {             // a pair that is not rotated has sine 0 and cosine 1
-            o[2 * i] = fmaf(n[2 * i], cs[r][i], -n[2 * i + 1] * sn[r][i]);
-            o[2 * i + 1] = fmaf(n[2 * i + 1], cs[r][i], n[2 * i] * sn[r][i]);
+        ss = ni_warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+        T* dst;
+        T* vdst = nullptr;
+        if (is_key) {
+            const size_t off = (((size_t)page * G + (head - H)) * page_size + (pos % page_size)) * D;
+            dst = k_pages + off;
+            vdst = v_pages + off;
+        } else {
+            dst = q_out + ((size_t)t * H + head) * D;
         }
-        Vec4<T>::store(dst + d0, o);
-        if (vdst != nullptr) Vec4<T>::store(vdst + d0, y[r]);
+#pragma unroll
+        for (int r = 0; r < CHUNKS; ++r) {
+            const int d0 = 4 * lane + 128 * r;
+            if (d0 >= D) continue;
+            float gn[4], n[4], o[4];
+            Vec4<float>::load(gain + d0, gn);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[i] = n[i] = y[r][i] * inv * gn[i];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (d0 + 2 * i < rot) {
+                    const float sn = s_sin[(d0 >> 1) + i], cs = s_cos[(d0 >> 1) + i];
+                    o[2 * i] = fmaf(n[2 * i], cs, -n[2 * i + 1] * sn);
+                    o[2 * i + 1] = fmaf(n[2 * i + 1], cs, n[2 * i] * sn);
+                }
+            }
+            Vec4<T>::store(dst + d0, o);
+            if (vdst != nullptr) Vec4<T>::store(vdst + d0, y[r]);
+        }
     }
 }
 
@@ -254,11 +247,13 @@ NI_EXPORT int ni_conv_qk_prepare(const void* proj, int dtype, int ld, const floa
         slots, block_table, bt_stride, inv_freq, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, H, G, D, rot,   \
         taps, page_size)
 #define LAUNCH_V(T, R)                                                                                          \
-    conv_qk_prepare_vec_kernel<T, R><<<(int)blocks, warps * 32, 0, stream>>>(                                   \
+    conv_qk_prepare_vec_kernel<T, R><<<vec_grid, vec_threads, 0, stream>>>(                                     \
         (const T*)proj, ld, conv_w, q_gain, k_gain, eps, state, state_stride, positions, seq_of_token, cu_q,    \
         slots, block_table, bt_stride, inv_freq, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, H, G, D, rot,   \
         taps, page_size)
     const bool vec = (D % 4 == 0) && (ld % 4 == 0);      // whole 8- or 16-byte pieces everywhere
+    const int vec_threads = 32 * (H + G < 8 ? H + G : 8);
+    const dim3 vec_grid(n_tokens, n_tokens < 4 * ni_sm_count() ? (H + G + 7) / 8 : 1);     // few tokens: a warp per head
 #define LAUNCH(T)                                          \
     do {                                                   \
         if (vec && D <= 128) LAUNCH_V(T, 1);               \

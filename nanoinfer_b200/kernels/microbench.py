@@ -7,6 +7,9 @@
     python -m nanoinfer_b200.kernels.microbench gemm_swap --m 64 --n 2048 --k 2048 --mode add --milestones
     python -m nanoinfer_b200.kernels.microbench decode_fused --batch 8 --context 2048
     python -m nanoinfer_b200.kernels.microbench delta_rule --batch 8 --tokens 1 --heads 16 --dim 128 --vdim 128
+    python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048 --q-heads 16 --head-dim 128 --score-cap 30
+    python -m nanoinfer_b200.kernels.microbench conv_attention --batch 1 --tokens 2048 --heads 16 --kv-heads 8 --dim 128
+    python -m nanoinfer_b200.kernels.microbench routed --tokens 2048 --width 2048 --ff 2048 --experts 16 --identity 2 --top 4
 
 Each case runs its kernel over several distinct copies of its inputs in turn (together
 larger than the L2 cache, so every run reads from HBM), times it with CUDA events after
@@ -204,7 +207,8 @@ def attention_decode(args) -> None:
     else:
         scratch = torch.empty(b * hq * splits * (hd + 2), dtype=torch.float32, device=DEV)
         fns = [lambda kc=kc, vc=vc: ops.attention_decode(q, kc, vc, out, None, b, positions, seq_of, table, hq, hkv, hd,
-                                                         page, None, 1.0 / math.sqrt(hd), splits, scratch, tickets)
+                                                         page, None, 1.0 / math.sqrt(hd), splits, scratch, tickets,
+                                                         score_cap=args.score_cap)
                for kc, vc in caches]
     us = _time(fns, args.iters)
     print(f"attention_decode{' (merge through scratch)' if args.scratch_merge else ''}{' (balanced)' if args.balanced else ''}{' ragged' if args.ragged else ''} batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
@@ -226,7 +230,7 @@ def attention_prefill(args) -> None:
     cu_q = torch.tensor([0, t], dtype=torch.int32, device=DEV)
     kv_len = torch.tensor([t], dtype=torch.int32, device=DEV)
     fn = lambda: ops.attention_prefill(q, kc, vc, out, tile_seq, tile_row0, len(tiles), cu_q, kv_len, table, hq, hkv,
-                                       hd, page, None, 1.0 / math.sqrt(hd), kernel=args.kernel)
+                                       hd, page, None, 1.0 / math.sqrt(hd), kernel=args.kernel, score_cap=args.score_cap)
     us = _time([fn], args.iters)
     ops.check_device_errors()
     flops = 4.0 * hq * hd * t * (t + 1) / 2
@@ -386,6 +390,90 @@ def delta_rule(args) -> None:
           f"gated norm {us_norm:.2f} us ({n * H * V * (4 + 4 + 2) / us_norm / 1e3:.0f} GB/s)")
 
 
+def conv_attention(args) -> None:
+    """What stands between the projection and the attention of a mixer with convolved queries and keys, at --batch
+    requests of --tokens tokens each: convolution + norm + rotation + cache write (and the history), then the
+    head gate and the normed addition of a sublayer's output into the stream."""
+    b, t, H, G, D, taps = args.batch, args.tokens, args.heads, args.kv_heads, args.dim, args.taps
+    n, page, width = b * t, 16, args.width
+    C = (H + G) * D
+    ld = -(-(C + H) // 8) * 8
+    bf = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(0)
+    copies = max(2, min(32, -(-2 * L2_BYTES // (n * (ld + 3 * C) * 2))))
+    projs = [torch.randn(n, ld, device=DEV, generator=g).to(bf) for _ in range(copies)]
+    conv_w = torch.randn(taps, C, device=DEV, generator=g) * 0.5
+    gain = torch.ones(D, device=DEV)
+    state = torch.zeros(b, (taps - 1) * C, device=DEV)
+    start = args.context
+    per_seq = -(-(start + t) // page)
+    k_pages = torch.zeros(b * per_seq, G, page, D, dtype=bf, device=DEV)
+    v_pages = torch.zeros_like(k_pages)
+    table = torch.randperm(b * per_seq, device=DEV, generator=g).int().view(b, per_seq)
+    pos = (torch.arange(t, device=DEV).repeat(b) + start).int()
+    seq = torch.repeat_interleave(torch.arange(b, device=DEV), t).int()
+    cu = torch.arange(0, n + 1, t, dtype=torch.int32, device=DEV)
+    slots = torch.arange(b, dtype=torch.int32, device=DEV)
+    inv_freq = torch.pow(500000.0, -2.0 * torch.arange(D // 4, device=DEV) / (D // 2)).float()
+    q = torch.empty(n, H * D, dtype=bf, device=DEV)
+    us = _time([lambda p=p: ops.conv_qk_prepare(p, conv_w, gain, gain, 1e-6, state, pos, seq, cu, slots, b, table, inv_freq, q,
+                                                k_pages, v_pages, H, G, D, D // 2, taps, page) for p in projs], args.iters)
+    moved = n * (C * 2 + (H + 2 * G) * D * 2)          # the channels read once, queries, keys and values written
+    att = [torch.randn(n, H * D, device=DEV, generator=g).to(bf) for _ in range(copies)]
+    us_gate = _time([lambda a=a, p=p: ops.head_gate(a, p, C, H, D) for a, p in zip(att, projs)], args.iters)
+    h = torch.zeros(n, width, device=DEV)
+    ys = [torch.randn(n, width, device=DEV, generator=g) for _ in range(max(2, min(32, -(-2 * L2_BYTES // (n * width * 4)))))]
+    gw = torch.ones(width, device=DEV)
+    us_add = _time([lambda y=y: ops.add_normed(h, y, gw, 1e-6) for y in ys], args.iters)
+    print(f"conv_attention batch={b} tokens={t} heads={H}/{G} dim={D} taps={taps}: prepare + history {us:.2f} us "
+          f"({moved / us / 1e3:.0f} GB/s), head gate {us_gate:.2f} us ({2 * n * H * D * 2 / us_gate / 1e3:.0f} GB/s), "
+          f"normed addition (width {width}) {us_add:.2f} us ({n * width * 12 / us_add / 1e3:.0f} GB/s)")
+
+
+def routed(args) -> None:
+    """The routed feed-forward at --tokens rows: the router, then the whole part (all its launches), in bfloat16."""
+    from ..config.model_config import FeedForwardSpec
+    from ..engine.runtime import Runtime
+    from ..parts.feed_forward import CappedGLU, RoutedExperts
+    n, d, f, E, I, top = args.tokens, args.width, args.ff, args.experts, args.identity, args.top
+    bf = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(0)
+    rt = Runtime(device=torch.device(DEV), dtype=bf, page_size=16)
+    ops.preload(["routed", "pointwise", "gemv_bf16", "gemv_ksplit"])
+    spec = FeedForwardSpec(kind="routed_experts", intermediate_size=f,
+                           extra=(("experts", E), ("identity_experts", I), ("top", top), ("choice_bias", True)))
+
+    def weights():
+        w = {"router": torch.randn(E + I, d, device=DEV, generator=g).to(bf) * (0.02 if args.flat_router else 0.5),
+             "correction": torch.randn(E + I, device=DEV, generator=g).to(bf) * 0.01}
+        for e in range(E):
+            for k, shape in (("gate", (f, d)), ("up", (f, d)), ("down", (d, f))):
+                w[f"e{e}.{k}"] = (torch.randn(shape, device=DEV, generator=g) * 0.02).to(bf)
+        return w
+    expert_bytes = E * 3 * f * d * 2
+    parts = [RoutedExperts(spec, d, weights(), rt) for _ in range(max(2, min(8, -(-2 * L2_BYTES // expert_bytes))))]
+    x = torch.randn(n, d, device=DEV, generator=g).to(bf)
+    ids = torch.empty(n, top, dtype=torch.int32, device=DEV)
+    wts = torch.empty(n, top, dtype=torch.float32, device=DEV)
+    us_route = _time([lambda p=p: ops.route(x, p.w_router, p.bias, ids, wts, None, E, top) for p in parts], args.iters)
+    for p in parts:
+        p.forward(x, None)                       # sizes the workspaces outside the captured loop
+    us_all = _time([lambda p=p: p.forward(x, None) for p in parts], args.iters)
+    chosen = torch.unique(ids[ids < E]).numel()
+    flops = 2.0 * (ids < E).sum().item() * 3 * f * d
+    print(f"routed tokens={n} width={d} expert ff={f} experts={E}+{I} top={top}: router {us_route:.2f} us; whole part "
+          f"{us_all:.2f} us ({chosen} of {E} experts chosen; {expert_bytes / us_all / 1e3:.0f} GB/s if every expert is read "
+          f"once, {flops / us_all / 1e6:.1f} TFLOP/s of chosen products)")
+    # the capped unit with as many weights per token, for comparison
+    dense = FeedForwardSpec(kind="capped_glu", intermediate_size=top * f, extra=(("limit", 7.0), ("gate_slope", 1.702), ("up_shift", 1.0)))
+    dparts = [CappedGLU(dense, d, {k: (torch.randn(shape, device=DEV, generator=g) * 0.02).to(bf)
+                                   for k, shape in (("gate", (top * f, d)), ("up", (top * f, d)), ("down", (d, top * f)))}, rt)
+              for _ in range(max(2, min(8, -(-2 * L2_BYTES // (3 * top * f * d * 2)))))]
+    us_dense = _time([lambda p=p: p.forward(x, None) for p in dparts], args.iters)
+    print(f"capped unit tokens={n} width={d} ff={top * f}: {us_dense:.2f} us ({3 * top * f * d * 2 / us_dense / 1e3:.0f} GB/s of "
+          f"weights, {2.0 * n * 3 * top * f * d / us_dense / 1e6:.1f} TFLOP/s)")
+
+
 def main() -> None:
     ops.require_cuda()
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -463,6 +551,7 @@ def main() -> None:
         p.add_argument("--page", type=int, default=16)
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--kernel", default=None, choices=["tc", "mma"], help="prefill: insist on one kernel")
+        p.add_argument("--score-cap", type=float, default=0.0, help="bound the scaled scores by cap * tanh(s / cap)")
         p.add_argument("--copies", type=int, default=0, help="decode: cache copies used in turn (default: enough to exceed L2; 1: the cache stays in L2)")
         p.add_argument("--balanced", action="store_true", help="decode: the kernel that deals the keys evenly over a fixed grid")
         p.add_argument("--ragged", action="store_true", help="decode: contexts from a quarter of --context up to it")
@@ -470,6 +559,25 @@ def main() -> None:
         p.add_argument("--scratch-merge", action="store_true",
                        help="decode: merge the splits through global scratch and tickets, not inside a cluster")
         p.set_defaults(fn=fn)
+    p = sub.add_parser("conv_attention")
+    p.add_argument("--batch", type=int, default=1)
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--context", type=int, default=0, help="tokens each request holds already")
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--dim", type=int, default=128)
+    p.add_argument("--taps", type=int, default=4)
+    p.add_argument("--width", type=int, default=2048)
+    p.set_defaults(fn=conv_attention)
+    p = sub.add_parser("routed")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--width", type=int, default=2048)
+    p.add_argument("--ff", type=int, default=2048, help="one expert's width")
+    p.add_argument("--experts", type=int, default=16)
+    p.add_argument("--identity", type=int, default=2)
+    p.add_argument("--top", type=int, default=4)
+    p.add_argument("--flat-router", action="store_true", help="router weights so small that the choice bias decides (all tokens choose alike)")
+    p.set_defaults(fn=routed)
     for sp in sub.choices.values():
         sp.add_argument("--iters", type=int, default=200)
     args = ap.parse_args()

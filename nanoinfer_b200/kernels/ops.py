@@ -535,7 +535,7 @@ def capped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: fl
 def conv_qk_prepare(proj, conv_w, q_gain, k_gain, eps, state, positions, seq_of_token, cu_q, slots, n_seqs, block_table,
                     inv_freq, q_out, k_pages, v_pages, n_heads, n_kv_heads, head_dim, rotary_dim, taps, page_size) -> None:
     """From the fused projection ``proj`` [T, ld] (columns: the queries' channels, the keys' channels, then whatever
-    else): causal convolution over time per channel (``conv_w`` float32 [C, taps], the last tap the token's own;
+    else): causal convolution over time per channel (``conv_w`` float32 [taps, C] - tap-major -, the last tap the token's own;
     what lies before a portion comes from the request's history in ``state`` float32 [slots, (taps - 1) C]), RMS
     norm per head (``q_gain`` / ``k_gain`` float32 [head_dim]), rotation of adjacent pairs of the first
     ``rotary_dim`` dimensions; queries -> q_out [T, H hd], keys -> k_pages, the keys' convolution output as it is ->
@@ -544,7 +544,7 @@ def conv_qk_prepare(proj, conv_w, q_gain, k_gain, eps, state, positions, seq_of_
     c = (n_heads + n_kv_heads) * head_dim
     write = k_pages is not None
     f32, i32 = torch.float32, torch.int32
-    if proj.shape[1] < c or q_out.shape != (n, n_heads * head_dim) or conv_w.shape != (c, taps):
+    if proj.shape[1] < c or q_out.shape != (n, n_heads * head_dim) or conv_w.shape != (taps, c):
         raise KernelError("conv_qk_prepare: shapes do not agree")
     if q_out.dtype != proj.dtype or (write and (k_pages.dtype != proj.dtype or v_pages.dtype != proj.dtype)):
         raise KernelError("conv_qk_prepare: all activations must share one dtype")

@@ -372,7 +372,7 @@ class ConvKeyAttention(PagedAttendMixin, Part):
             rows.append(torch.zeros(pad, hidden_size, dtype=weights["q"].dtype, device=weights["q"].device))
         self.w_in = rt.weight(torch.cat(rows, dim=0))
         self.w_o = rt.weight(weights["o"])
-        self.conv_w = rt.gain(torch.cat([weights["q.conv"], weights["k.conv"]], dim=0))
+        self.conv_w = rt.gain(torch.cat([weights["q.conv"], weights["k.conv"]], dim=0).t())      # tap-major [taps, C]
         self.q_gain, self.k_gain = rt.gain(weights["q.norm"]), rt.gain(weights["k.norm"])
         self._no_state = torch.zeros((1, 0), dtype=torch.float32, device=rt.device)
 

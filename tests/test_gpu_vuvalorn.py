@@ -198,7 +198,7 @@ def test_convolution_norm_rotation_and_cache_write(H, G, D, taps, rot, dtype):
     v_pages = torch.zeros_like(k_pages)
     q_out = torch.empty(n, H * D, dtype=dtype, device=DEV)
     state_d = state.to(DEV)
-    ops.conv_qk_prepare(proj.to(DEV), conv_w.to(DEV), qg.to(DEV), kg.to(DEV), eps, state_d, positions.to(DEV),
+    ops.conv_qk_prepare(proj.to(DEV), conv_w.t().contiguous().to(DEV), qg.to(DEV), kg.to(DEV), eps, state_d, positions.to(DEV),
                         seq_of.to(DEV), cu.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV), 3, table.to(DEV),
                         inv_freq.to(DEV), q_out, k_pages, v_pages, H, G, D, rot, taps, page)
     tol = _tol(dtype)
