@@ -328,6 +328,56 @@ __global__ void combine_add_normed_kernel(const T* __restrict__ z, const T* __re
     for (int c = threadIdx.x; c < d; c += blockDim.x) h[(size_t)t * d + c] += ys[c] * inv * gain[c];
 }
 
+// The same, 16 bytes per thread (widths that are multiples of 8 bfloat16 or 4 float values; at most 256 choices):
+// the token's weights and rows are looked up once into shared memory.
+template <typename T>
+__global__ void combine_add_normed_vec_kernel(const T* __restrict__ z, const T* __restrict__ x, const int* __restrict__ ids,
+                                              const float* __restrict__ weights, const int* __restrict__ row_of_pair,
+                                              float* __restrict__ h, const float* __restrict__ gain, float eps, int d, int top,
+                                              int n_real, int all_experts) {
+    constexpr int V = NiVec16<T>::N;
+    extern __shared__ __align__(16) float ys[];          // [d]
+    __shared__ float scratch[32];
+    __shared__ float s_w[RT_MAX_EXPERTS];
+    __shared__ int s_row[RT_MAX_EXPERTS];
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < top; j += blockDim.x) {
+        const int p = t * top + j, e = ids[p];
+        s_w[j] = weights[p];
+        s_row[j] = e >= n_real ? -1 : (all_experts > 0 ? t * all_experts + e : (row_of_pair ? row_of_pair[p] : p));
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int c = threadIdx.x * V; c < d; c += blockDim.x * V) {
+        float acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int row = s_row[j];
+            float v[V];
+            NiVec16<T>::load((row < 0 ? x + (size_t)t * d : z + (size_t)row * d) + c, v);
+            const float wgt = s_w[j];
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] = fmaf(wgt, v[k], acc[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            ys[c + k] = acc[k];
+            ss += acc[k] * acc[k];
+        }
+    }
+    ss = ni_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+        float a[4], g[4];
+        NiVec16<float>::load(h + (size_t)t * d + c, a);
+        NiVec16<float>::load(gain + c, g);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a[k] += ys[c + k] * inv * g[k];
+        NiVec16<float>::store(h + (size_t)t * d + c, a);
+    }
+}
+
 NI_EXPORT int ni_route(const void* x, int dtype, const float* w_router, const float* bias, int* ids, float* weights,
                        int* counts, int n_tokens, int d, int n_all, int n_real, int top, int renormalize,
                        cudaStream_t stream) {
@@ -402,6 +452,16 @@ NI_EXPORT int ni_route_combine_add_normed(const void* z, const void* x, int dtyp
     if (d > 12000) return NI_ERR_UNSUPPORTED_SIZE;
     const int threads = d >= 1024 ? 256 : 128;
     const size_t smem = (size_t)d * sizeof(float);
+    if (top <= RT_MAX_EXPERTS && dtype == NI_DTYPE_BF16 && d % 8 == 0) {
+        combine_add_normed_vec_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
+            (const __nv_bfloat16*)z, (const __nv_bfloat16*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+        NI_RETURN_LAUNCH_STATUS();
+    }
+    if (top <= RT_MAX_EXPERTS && dtype == NI_DTYPE_F32 && d % 4 == 0) {
+        combine_add_normed_vec_kernel<float><<<n_tokens, threads, smem, stream>>>(
+            (const float*)z, (const float*)x, ids, weights, row_of_pair, h, gain, eps, d, top, n_real, all_experts);
+        NI_RETURN_LAUNCH_STATUS();
+    }
     if (dtype == NI_DTYPE_F32)
         combine_add_normed_kernel<float><<<n_tokens, threads, smem, stream>>>((const float*)z, (const float*)x, ids, weights,
                                                                              row_of_pair, h, gain, eps, d, top, n_real, all_experts);

@@ -431,7 +431,8 @@ def conv_attention(args) -> None:
 
 
 def routed(args) -> None:
-    """The routed feed-forward at --tokens rows: the router, then the whole part (all its launches), in bfloat16."""
+    """The routed feed-forward at --tokens rows: the router, then the whole part (all its launches, its output normed
+    and added into an FP32 stream as a sandwich layer asks for it), in bfloat16."""
     from ..config.model_config import FeedForwardSpec
     from ..engine.runtime import Runtime
     from ..parts.feed_forward import CappedGLU, RoutedExperts
@@ -456,9 +457,10 @@ def routed(args) -> None:
     ids = torch.empty(n, top, dtype=torch.int32, device=DEV)
     wts = torch.empty(n, top, dtype=torch.float32, device=DEV)
     us_route = _time([lambda p=p: ops.route(x, p.w_router, p.bias, ids, wts, None, E, top) for p in parts], args.iters)
+    h, gain = torch.zeros(n, d, device=DEV), torch.ones(d, device=DEV)
     for p in parts:
-        p.forward(x, None)                       # sizes the workspaces outside the captured loop
-    us_all = _time([lambda p=p: p.forward(x, None) for p in parts], args.iters)
+        p.forward(x, None, normed_into=(h, gain, 1e-6))                       # sizes the workspaces outside the captured loop
+    us_all = _time([lambda p=p: p.forward(x, None, normed_into=(h, gain, 1e-6)) for p in parts], args.iters)
     chosen = torch.unique(ids[ids < E]).numel()
     flops = 2.0 * (ids < E).sum().item() * 3 * f * d
     print(f"routed tokens={n} width={d} expert ff={f} experts={E}+{I} top={top}: router {us_route:.2f} us; whole part "
@@ -469,7 +471,7 @@ def routed(args) -> None:
     dparts = [CappedGLU(dense, d, {k: (torch.randn(shape, device=DEV, generator=g) * 0.02).to(bf)
                                    for k, shape in (("gate", (top * f, d)), ("up", (top * f, d)), ("down", (d, top * f)))}, rt)
               for _ in range(max(2, min(8, -(-2 * L2_BYTES // (3 * top * f * d * 2)))))]
-    us_dense = _time([lambda p=p: p.forward(x, None) for p in dparts], args.iters)
+    us_dense = _time([lambda p=p: ops.add_normed(h, p.forward(x, None), gain, 1e-6) for p in dparts], args.iters)
     print(f"capped unit tokens={n} width={d} ff={top * f}: {us_dense:.2f} us ({3 * top * f * d * 2 / us_dense / 1e3:.0f} GB/s of "
           f"weights, {2.0 * n * 3 * top * f * d / us_dense / 1e6:.1f} TFLOP/s)")
 

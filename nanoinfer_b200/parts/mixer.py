@@ -359,6 +359,8 @@ class ConvKeyAttention(PagedAttendMixin, Part):
         self.window = None
         self.scale = float(spec.softmax_scale)
         self.score_cap = float(e.get("score_cap", 0.0))
+        if self.score_cap == 0.0 and rt.dtype == torch.bfloat16:
+            self.kernel_modules = ("attention_prefill_tc",)      # without a cap, prompt portions may take the tcgen05 kernel
         self.eps = float(e.get("norm_eps", 1e-6))
         self.position = part("position", spec.position.kind)(spec.position, hidden_size, {}, rt)
         if self.position.rotary_dim > d or (self.position.rotary_dim > 0 and not self.position.interleaved):
